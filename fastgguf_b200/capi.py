@@ -244,8 +244,33 @@ def prompts_arrays(prompts):
     return (c_int * max(1, len(flat)))(*flat), (c_int64 * len(offs))(*offs)
 
 
-def ensure_kernel_libraries(dtype_code: int) -> None:
-    """Build (if stale) the kernel libraries an engine of this dtype opens by name."""
+def kernel_modules_for(spec_json, dtype_code: int) -> tuple:
+    """The kernel libraries a model needs: the row-wise and any-size kernels always; the tensor-core contraction in
+    bfloat16; the tensor-core attention where a mixer's sizes fit it; retention and the experts where the model has them.
+    Without a spec: everything the dtype can use."""
+    modules = ["core"] + (["tc"] if dtype_code == FG_BF16 else [])
+    if spec_json is None:
+        return tuple(modules + (["attn"] if dtype_code == FG_BF16 else []) + ["mix"])
+    kinds = set()
+    fast_attention = False
+    for layer in spec_json.get("layers", []):
+        for role in ("mixer", "feed_forward"):
+            part = layer.get(role) or {}
+            kinds.add(part.get("kind"))
+            p = part.get("params") or {}
+            if role == "mixer" and part.get("kind") == "gqa_attention" and p.get("head_dim") in (64, 128) and p.get("v_head_dim", p.get("head_dim")) == p.get("head_dim") \
+                    and not (p.get("window") and p.get("keep_first")):
+                fast_attention = True
+    builtin = {"gqa_attention", "swiglu", "retention", "mlp", "moe", None}
+    if dtype_code == FG_BF16 and (fast_attention or kinds - builtin):
+        modules.append("attn")
+    if kinds & {"retention", "moe"}:
+        modules.append("mix")
+    return tuple(modules)
+
+
+def ensure_kernel_libraries(dtype_code: int, spec_json=None) -> None:
+    """Build (if stale) the kernel libraries an engine of this dtype and model opens by name."""
     from .csrc.build import build_module
-    for module in (("core", "tc", "attn") if dtype_code == FG_BF16 else ("core",)):
+    for module in kernel_modules_for(spec_json, dtype_code):
         build_module(module)

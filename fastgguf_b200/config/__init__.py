@@ -1,5 +1,6 @@
 """Typed configurations, chosen by ``architectures[0]`` of config.json (read and checked by the C++ host)."""
 from .base import ConfigError, ModelConfig, architecture_name, read_config_json
 from .llama import LlamaConfig
+from .zirivik import ZirivikConfig
 
-__all__ = ["ConfigError", "ModelConfig", "LlamaConfig", "architecture_name", "read_config_json"]
+__all__ = ["ConfigError", "ModelConfig", "LlamaConfig", "ZirivikConfig", "architecture_name", "read_config_json"]

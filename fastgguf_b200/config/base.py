@@ -107,6 +107,8 @@ def read_config_json(model_dir: str) -> dict:
 
 def architecture_name(d: dict) -> str:
     archs = d.get("architectures")
+    if archs is None and isinstance(d.get("architecture"), str):
+        return d["architecture"]
     if not isinstance(archs, list) or not archs or not isinstance(archs[0], str):
-        raise ConfigError("config.json: 'architectures' must be a non-empty list of names")
+        raise ConfigError("config.json: 'architectures' must be a non-empty list of names (or 'architecture' a name)")
     return archs[0]

@@ -5,8 +5,10 @@
 // (:3246, :3317), the mask is the loop range (:4782, :5030-5035), softmax with max
 // subtraction (:3147-3156), o = sum_p w_p V[p] (:3320-3323); query head h uses KV head
 // h / (H / KV) (:4781).  A window of w keeps only the last w positions (:4754-4758).
+// keep_first > 0 adds the sequence's first keep_first positions to what a windowed row sees (they keep
+// their places; a row sees each key once).  Values may have another size (hdv) than keys (hd).
 //
-// Keys are visited in chunks of CHUNK positions counted from lo, with a running maximum and
+// Keys are visited in chunks of CHUNK visible keys, the kept first ones and then the window from lo, with a running maximum and
 // sum in f32 (online softmax).  Within a chunk a thread scores whole keys; for the weighted sum of
 // values the chunk's keys are dealt to the warps in equal runs, every lane owns output dimensions
 // (lane, lane + 32, ...), and the warps' partial sums are added in warp order.  All of that depends
@@ -25,7 +27,7 @@ attention_generic_kernel(const T *__restrict__ q, int ldq, T *__restrict__ out, 
                          const int *__restrict__ positions, const int *__restrict__ row_seq,
                          const int *__restrict__ block_table, int table_width,
                          const T *__restrict__ k_pool, const T *__restrict__ v_pool,
-                         int H, int KV, int hd, int page_size, float scale, int window) {
+                         int H, int KV, int hd, int hdv, int page_size, float scale, int window, int keep_first) {
     extern __shared__ float smem[];
     float *qs = smem;                 // [hd]
     float *sc = smem + hd;            // [CHUNK]
@@ -34,22 +36,24 @@ attention_generic_kernel(const T *__restrict__ q, int ldq, T *__restrict__ out, 
     int kvh = h / (H / KV);
     int pos = positions[m];
     int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int n_first = min(keep_first, lo);          // kept first keys that lie in front of the window
+    const int n_keys = n_first + pos - lo + 1;        // visible key v is position v (v < n_first) or lo + v - n_first
     const int *bt = block_table + (size_t)row_seq[m] * table_width;
     const T *qrow = q + (size_t)m * ldq + (size_t)h * hd;
     for (int d = threadIdx.x; d < hd; d += ATT_THREADS) qs[d] = to_f32<T>(qrow[d]);
     __syncthreads();
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    float *part = sc + CHUNK;         // [ATT_WARPS][hd] partial value sums of a chunk
+    float *part = sc + CHUNK;         // [ATT_WARPS][hdv] partial value sums of a chunk
     float m_run = -INFINITY, l_run = 0.f;
     float acc[DPL];               // warp 0 keeps the running output: dims lane + 32 j
 #pragma unroll
     for (int j = 0; j < DPL; j++) acc[j] = 0.f;
-    for (int c0 = lo; c0 <= pos; c0 += CHUNK) {
-        int n = min(CHUNK, pos - c0 + 1);
+    for (int c0 = 0; c0 < n_keys; c0 += CHUNK) {
+        int n = min(CHUNK, n_keys - c0);
         float cmax = -INFINITY;
         for (int i = threadIdx.x; i < n; i += ATT_THREADS) {
-            int p = c0 + i;
+            int p = c0 + i < n_first ? c0 + i : lo + (c0 + i - n_first);
             const T *kr = k_pool + (((size_t)bt[p / page_size] * KV + kvh) * page_size + p % page_size) * hd;
             float s = 0.f;
             if (sizeof(T) == 4 && (hd & 3) == 0) {
@@ -86,9 +90,11 @@ attention_generic_kernel(const T *__restrict__ q, int ldq, T *__restrict__ out, 
 #pragma unroll
         for (int j = 0; j < DPL; j++) pv[j] = 0.f;
         for (int i = warp * run; i < i_end;) {
-            const int p = c0 + i, off = p % page_size;
-            const int cnt = min(page_size - off, i_end - i);
-            const T *vr = v_pool + (((size_t)bt[p / page_size] * KV + kvh) * page_size + off) * hd;
+            const int vi = c0 + i;
+            const int p = vi < n_first ? vi : lo + (vi - n_first), off = p % page_size;
+            // a run of keys within one page, and within the kept first keys or within the window
+            const int cnt = min(min(page_size - off, i_end - i), vi < n_first ? n_first - vi : i_end - i);
+            const T *vr = v_pool + (((size_t)bt[p / page_size] * KV + kvh) * page_size + off) * hdv;
             for (int u0 = 0; u0 < cnt; u0 += 8) {
                 float v[8][DPL];
 #pragma unroll
@@ -96,7 +102,7 @@ attention_generic_kernel(const T *__restrict__ q, int ldq, T *__restrict__ out, 
 #pragma unroll
                     for (int j = 0; j < DPL; j++) {
                         const int d = lane + 32 * j;
-                        v[u][j] = (u0 + u < cnt && d < hd) ? to_f32<T>(vr[(size_t)(u0 + u) * hd + d]) : 0.f;
+                        v[u][j] = (u0 + u < cnt && d < hdv) ? to_f32<T>(vr[(size_t)(u0 + u) * hdv + d]) : 0.f;
                     }
 #pragma unroll
                 for (int u = 0; u < 8; u++) {
@@ -110,15 +116,15 @@ attention_generic_kernel(const T *__restrict__ q, int ldq, T *__restrict__ out, 
         }
 #pragma unroll
         for (int j = 0; j < DPL; j++)
-            if (lane + 32 * j < hd) part[warp * hd + lane + 32 * j] = pv[j];
+            if (lane + 32 * j < hdv) part[warp * hdv + lane + 32 * j] = pv[j];
         __syncthreads();
         if (warp == 0) {
 #pragma unroll
             for (int j = 0; j < DPL; j++) {
                 const int d = lane + 32 * j;
-                if (d >= hd) break;
+                if (d >= hdv) break;
                 float t = 0.f;
-                for (int w = 0; w < ATT_WARPS; w++) t += part[w * hd + d];      // warp order
+                for (int w = 0; w < ATT_WARPS; w++) t += part[w * hdv + d];     // warp order
                 acc[j] = acc[j] * corr + t;
             }
         }
@@ -126,12 +132,34 @@ attention_generic_kernel(const T *__restrict__ q, int ldq, T *__restrict__ out, 
         __syncthreads();                   // sc[] and part[] are rewritten by the next chunk
     }
     if (warp == 0) {
-        T *orow = out + (size_t)m * ldo + (size_t)h * hd;
+        T *orow = out + (size_t)m * ldo + (size_t)h * hdv;
         const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
 #pragma unroll
         for (int j = 0; j < DPL; j++)
-            if (lane + 32 * j < hd) orow[lane + 32 * j] = from_f32<T>(acc[j] * inv);
+            if (lane + 32 * j < hdv) orow[lane + 32 * j] = from_f32<T>(acc[j] * inv);
     }
+}
+
+extern "C" int fg_attention_generic_kept(const void *q, int ldq, void *out, int ldo, int dtype,
+                                         const int *positions, const int *row_seq, const int *block_table,
+                                         int table_width, const void *k_pool, const void *v_pool,
+                                         int M, int H, int KV, int hd, int hdv, int page_size, float scale, int window,
+                                         int keep_first, cudaStream_t stream) {
+    if (M <= 0) return 0;
+    const int big = hd > hdv ? hd : hdv;
+    if (big > 32 * MAX_DPL || hd <= 0 || hdv <= 0 || H % KV != 0 || H > 65535 || keep_first < 0) return FG_ERR_BAD_SIZE;
+    dim3 grid(M, H);
+    size_t smem = (size_t)(hd + CHUNK + ATT_WARPS * hdv) * sizeof(float);
+#define ATT_LAUNCH(T, DPL) attention_generic_kernel<T, DPL><<<grid, ATT_THREADS, smem, stream>>>((const T *)q, ldq, (T *)out, ldo, \
+        positions, row_seq, block_table, table_width, (const T *)k_pool, (const T *)v_pool, H, KV, hd, hdv, page_size, scale, window, \
+        window > 0 ? keep_first : 0)
+#define ATT_BY_SIZE(T) do { if (hdv <= 64) ATT_LAUNCH(T, 2); else if (hdv <= 128) ATT_LAUNCH(T, 4); else ATT_LAUNCH(T, 8); } while (0)
+    if (dtype == FG_F32) ATT_BY_SIZE(float);
+    else if (dtype == FG_BF16) ATT_BY_SIZE(bf16);
+    else return FG_ERR_BAD_DTYPE;
+#undef ATT_BY_SIZE
+#undef ATT_LAUNCH
+    return FG_LAUNCH_CHECK();
 }
 
 extern "C" int fg_attention_generic(const void *q, int ldq, void *out, int ldo, int dtype,
@@ -139,17 +167,6 @@ extern "C" int fg_attention_generic(const void *q, int ldq, void *out, int ldo, 
                                     int table_width, const void *k_pool, const void *v_pool,
                                     int M, int H, int KV, int hd, int page_size, float scale, int window,
                                     cudaStream_t stream) {
-    if (M <= 0) return 0;
-    if (hd > 32 * MAX_DPL || hd <= 0 || H % KV != 0 || H > 65535) return FG_ERR_BAD_SIZE;
-    dim3 grid(M, H);
-    size_t smem = (size_t)(hd + CHUNK + ATT_WARPS * hd) * sizeof(float);
-#define ATT_LAUNCH(T, DPL) attention_generic_kernel<T, DPL><<<grid, ATT_THREADS, smem, stream>>>((const T *)q, ldq, (T *)out, ldo, \
-        positions, row_seq, block_table, table_width, (const T *)k_pool, (const T *)v_pool, H, KV, hd, page_size, scale, window)
-#define ATT_BY_SIZE(T) do { if (hd <= 64) ATT_LAUNCH(T, 2); else if (hd <= 128) ATT_LAUNCH(T, 4); else ATT_LAUNCH(T, 8); } while (0)
-    if (dtype == FG_F32) ATT_BY_SIZE(float);
-    else if (dtype == FG_BF16) ATT_BY_SIZE(bf16);
-    else return FG_ERR_BAD_DTYPE;
-#undef ATT_BY_SIZE
-#undef ATT_LAUNCH
-    return FG_LAUNCH_CHECK();
+    return fg_attention_generic_kept(q, ldq, out, ldo, dtype, positions, row_seq, block_table, table_width, k_pool, v_pool, M, H, KV,
+                                     hd, hd, page_size, scale, window, 0, stream);
 }

@@ -246,6 +246,136 @@ extern "C" int fg_rope_append(void *qkv, int dtype, int ld, const int *positions
     return FG_LAUNCH_CHECK();
 }
 
+// ------------------------------------------------------------------ cache append without rotation
+// For mixers whose scores do not depend on positions, and whose values may be of another size than their
+// keys: k heads [KV, hd] and v heads [KV, hdv] of each row are copied to the row's place in its page.
+// qkv rows: (q heads | k heads | v heads).  Pools: k [n_pages, KV, P, hd], v [n_pages, KV, P, hdv].
+template <typename T>
+__global__ void kv_append_kernel(const T *__restrict__ qkv, int ld, int k_off, const int *__restrict__ positions,
+                                 const int *__restrict__ row_seq, const int *__restrict__ block_table, int table_width,
+                                 T *__restrict__ k_pool, T *__restrict__ v_pool, int KV, int hd, int hdv, int page_size) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int m = blockIdx.x, pos = positions[m];
+    const int page = block_table[(size_t)row_seq[m] * table_width + pos / page_size], off = pos % page_size;
+    const T *krow = qkv + (size_t)m * ld + k_off, *vrow = krow + (size_t)KV * hd;
+    for (int i = threadIdx.x; i < KV * hd; i += blockDim.x) {
+        int h = i / hd, d = i - h * hd;
+        k_pool[(((size_t)page * KV + h) * page_size + off) * hd + d] = krow[i];
+    }
+    for (int i = threadIdx.x; i < KV * hdv; i += blockDim.x) {
+        int h = i / hdv, d = i - h * hdv;
+        v_pool[(((size_t)page * KV + h) * page_size + off) * hdv + d] = vrow[i];
+    }
+}
+
+extern "C" int fg_kv_append(const void *qkv, int dtype, int ld, int k_off, const int *positions, const int *row_seq,
+                            const int *block_table, int table_width, void *k_pool, void *v_pool, int M, int KV, int hd,
+                            int hdv, int page_size, cudaStream_t stream) {
+    if (M <= 0) return 0;
+    int work = KV * (hd > hdv ? hd : hdv);
+    int threads = work >= 1024 ? 256 : (work >= 128 ? 128 : 64);
+    if (dtype == FG_F32)
+        return fg_launch(kv_append_kernel<float>, dim3(M), dim3(threads), 0, stream, (const float *)qkv, ld, k_off, positions, row_seq,
+                         block_table, table_width, (float *)k_pool, (float *)v_pool, KV, hd, hdv, page_size);
+    if (dtype == FG_BF16)
+        return fg_launch(kv_append_kernel<bf16>, dim3(M), dim3(threads), 0, stream, (const bf16 *)qkv, ld, k_off, positions, row_seq,
+                         block_table, table_width, (bf16 *)k_pool, (bf16 *)v_pool, KV, hd, hdv, page_size);
+    return FG_ERR_BAD_DTYPE;
+}
+
+// ------------------------------------------------------------------ norm of a sublayer's output, residual add, next norm
+// For blocks that normalise a sublayer's output before adding it: x[m] += t[m] / rms(t[m]) * w_post, and,
+// when w_next is given, out[m] = x[m] / rms(x[m]) * w_next for the sublayer that reads x next - one pass over
+// the row instead of three kernels.  Statistics and the sum are 32-bit; one block a row, fixed reduction order.
+template <typename TO>
+__global__ void norm_add_norm_kernel(const float *__restrict__ t, const float *__restrict__ w_post, float *__restrict__ x,
+                                     const float *__restrict__ w_next, TO *__restrict__ out, int E, float eps_post,
+                                     float eps_next) {
+    __shared__ float scratch[32];
+    extern __shared__ float row[];        // [E] the updated residual row, when a next norm is wanted
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t base = (size_t)blockIdx.x * E;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < E; i += blockDim.x) { float v = t[base + i]; ss += v * v; }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)E + eps_post);
+    float ss2 = 0.f;
+    for (int i = threadIdx.x; i < E; i += blockDim.x) {
+        float v = x[base + i] + t[base + i] * inv * w_post[i];
+        x[base + i] = v;
+        if (w_next) { row[i] = v; ss2 += v * v; }
+    }
+    if (!w_next) return;
+    ss2 = block_sum(ss2, scratch);
+    const float inv2 = 1.0f / sqrtf(ss2 / (float)E + eps_next);
+    for (int i = threadIdx.x; i < E; i += blockDim.x) out[base + i] = from_f32<TO>(row[i] * inv2 * w_next[i]);
+}
+
+extern "C" int fg_norm_add_norm(const float *t, const float *w_post, float *x, const float *w_next, void *out, int out_dtype,
+                                int M, int E, float eps_post, float eps_next, cudaStream_t stream) {
+    if (M <= 0) return 0;
+    int threads = E >= 2048 ? 256 : (E >= 512 ? 128 : 64);
+    size_t smem = w_next ? (size_t)E * sizeof(float) : 0;
+    if (smem > 48 * 1024) return FG_ERR_BAD_SIZE;
+    if (out_dtype == FG_F32 || !w_next)
+        return fg_launch(norm_add_norm_kernel<float>, dim3(M), dim3(threads), smem, stream, t, w_post, x, w_next, (float *)out, E,
+                         eps_post, eps_next);
+    if (out_dtype == FG_BF16)
+        return fg_launch(norm_add_norm_kernel<bf16>, dim3(M), dim3(threads), smem, stream, t, w_post, x, w_next, (bf16 *)out, E,
+                         eps_post, eps_next);
+    return FG_ERR_BAD_DTYPE;
+}
+
+// ------------------------------------------------------------------ activations in place
+// kind 0: relu(z)^2.  In f32; the result is stored in the buffer's dtype.
+template <typename T>
+__global__ void activation_kernel(T *__restrict__ z, size_t total, int kind) {
+    pdl_launch_dependents();
+    pdl_wait();
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; i < total; i += stride) {
+        float v = to_f32<T>(z[i]);
+        v = v > 0.f ? v * v : 0.f;
+        z[i] = from_f32<T>(v);
+    }
+}
+
+extern "C" int fg_activation(void *z, int dtype, long long total, int kind, cudaStream_t stream) {
+    if (total <= 0) return 0;
+    if (kind != 0) return FG_ERR_BAD_SIZE;
+    size_t want = ((size_t)total + 255) / 256;
+    int blocks = (int)(want > 148 * 16 ? 148 * 16 : want);
+    if (dtype == FG_F32) return fg_launch(activation_kernel<float>, dim3(blocks), dim3(256), 0, stream, (float *)z, (size_t)total, kind);
+    if (dtype == FG_BF16) return fg_launch(activation_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (bf16 *)z, (size_t)total, kind);
+    return FG_ERR_BAD_DTYPE;
+}
+
+// ------------------------------------------------------------------ soft cap of logits
+// z <- cap * tanh(z / cap), in place on float32 logits [R, V] with row stride ld.
+__global__ void softcap_kernel(float *__restrict__ z, int V, int ld, size_t total, float cap, float inv_cap) {
+    pdl_launch_dependents();
+    pdl_wait();
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; i < total; i += stride) {
+        size_t r = i / V;
+        float *p = z + r * ld + (i - r * V);
+        *p = cap * tanhf(*p * inv_cap);
+    }
+}
+
+extern "C" int fg_softcap(float *logits, int R, int V, int ld, float cap, cudaStream_t stream) {
+    size_t total = (size_t)R * V;
+    if (total == 0) return 0;
+    if (!(cap > 0.f)) return FG_ERR_BAD_SIZE;
+    size_t want = (total + 255) / 256;
+    int blocks = (int)(want > 148 * 16 ? 148 * 16 : want);
+    return fg_launch(softcap_kernel, dim3(blocks), dim3(256), 0, stream, logits, V, ld, total, cap, 1.0f / cap);
+}
+
 // ------------------------------------------------------------------ SiLU(g) * u
 // gu: [M, 2F] rows of (gate | up); out: [M, F].
 template <typename T>

@@ -1,0 +1,252 @@
+// Mixture of experts: routing, the experts' contractions over rows grouped by expert, and the sum.
+//
+//   scores s = sigmoid(z) of the router logits z (float32); a row uses the `top` experts with the largest scores, each
+//   weighted by its own score (kind 0: as it is, not renormalised).  The weight multiplies the expert's INPUT:
+//       out = sum_e expert_e(s_e h),   expert(x) = W_down act(W_gate x, W_up x)
+//   and since both first contractions are linear in x, s_e is applied to their float32 results instead of to h.
+//   act, kind 0:  g = min(g, limit), u = clamp(u, -limit, limit), y = g * sigmoid(alpha g) * (u + 1).
+//
+// Layout.  A "pair" p = row * top + k is a row's k-th choice.  route() writes the pair's expert and weight and groups
+// pairs by expert: `order[slot] = pair`, `slot_of[pair] = slot`, expert e owning slots [offsets[e], offsets[e + 1]).
+// The contractions run over slots, so that a tile of rows shares one expert's weights; all sizes that depend on the
+// routing stay on the device (nothing is read back).  An output element is summed along k in the same order whichever
+// tile or slot its row lands in, and a row's experts are added in the order of its choices, so a row's result does not
+// depend on what else is in the step.
+//
+// Weights: w_in [X, 2F, E] (gate rows, then up rows, of each expert), w_out [X, E, F]; activations and weights share
+// the engine's dtype T, accumulation is float32.
+#include "common.cuh"
+
+#define MOE_MAX_EXPERTS 256
+#define MOE_MAX_TOP 8
+
+// ------------------------------------------------------------------ routing
+// One block.  logits: [M, X] float32.
+__global__ void __launch_bounds__(1024)
+moe_route_kernel(const float *__restrict__ logits, int M, int X, int top, int *__restrict__ pair_expert, float *__restrict__ pair_weight,
+                 int *__restrict__ offsets, int *__restrict__ order, int *__restrict__ slot_of) {
+    __shared__ int counts[MOE_MAX_EXPERTS], cursor[MOE_MAX_EXPERTS];
+    pdl_launch_dependents();
+    pdl_wait();
+    for (int e = threadIdx.x; e < X; e += blockDim.x) counts[e] = 0;
+    __syncthreads();
+    for (int r = threadIdx.x; r < M; r += blockDim.x) {
+        const float *z = logits + (size_t)r * X;
+        int chosen[MOE_MAX_TOP];
+        for (int k = 0; k < top; k++) {
+            int best = -1;
+            float bz = 0.f;
+            for (int e = 0; e < X; e++) {
+                bool taken = false;
+                for (int q = 0; q < k; q++) taken = taken || chosen[q] == e;
+                if (taken) continue;
+                float v = z[e];
+                if (best < 0 || v > bz) { best = e; bz = v; }       // sigmoid is monotonic: the largest logit; ties to the lower index
+            }
+            chosen[k] = best;
+            pair_expert[(size_t)r * top + k] = best;
+            pair_weight[(size_t)r * top + k] = 1.0f / (1.0f + expf(-bz));
+            atomicAdd(&counts[best], 1);
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0;
+        for (int e = 0; e < X; e++) { offsets[e] = at; cursor[e] = at; at += counts[e]; }
+        offsets[X] = at;
+    }
+    __syncthreads();
+    for (int p = threadIdx.x; p < M * top; p += blockDim.x) {
+        int slot = atomicAdd(&cursor[pair_expert[p]], 1);
+        order[slot] = p;
+        slot_of[p] = slot;
+    }
+}
+
+extern "C" int fg_moe_route(const float *logits, int M, int X, int top, int *pair_expert, float *pair_weight, int *offsets, int *order,
+                            int *slot_of, cudaStream_t stream) {
+    if (M <= 0) return 0;
+    if (X <= 0 || X > MOE_MAX_EXPERTS || top <= 0 || top > MOE_MAX_TOP || top > X) return FG_ERR_BAD_SIZE;
+    int threads = M >= 1024 ? 1024 : ((M + 31) / 32) * 32;
+    return fg_launch(moe_route_kernel, dim3(1), dim3(threads), 0, stream, logits, M, X, top, pair_expert, pair_weight, offsets, order,
+                     slot_of);
+}
+
+__device__ __forceinline__ float expert_act(float g, float u, float limit, float alpha) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g / (1.0f + expf(-alpha * g)) * (u + 1.0f);
+}
+
+// ------------------------------------------------------------------ tiles of 64 slots x 64 outputs on the FMA units
+// The tile of a block: walk the experts, each padded to whole tiles; blocks beyond the last tile leave.
+#define MT 64
+#define MK 16
+
+__device__ __forceinline__ bool moe_find_tile(const int *__restrict__ offsets, int X, int tile, int *expert, int *slot0, int *slot1) {
+    for (int e = 0; e < X; e++) {
+        const int a = offsets[e], b = offsets[e + 1], nt = (b - a + MT - 1) / MT;
+        if (tile < nt) { *expert = e; *slot0 = a + tile * MT; *slot1 = min(b, a + (tile + 1) * MT); return true; }
+        tile -= nt;
+    }
+    return false;
+}
+
+// FIRST: y[slot, n] = act(w (x . gate_n), w (x . up_n)) with x = xn[pair / top]; else out[slot, n] = y[slot] . down_n
+template <typename T, bool FIRST>
+__global__ void __launch_bounds__(256)
+moe_tile_kernel(const T *__restrict__ A, int lda, const T *__restrict__ W, void *__restrict__ out, int ldo,
+                const int *__restrict__ offsets, const int *__restrict__ order, const float *__restrict__ pair_weight, int X, int top,
+                int N, int K, float limit, float alpha) {
+    __shared__ float As[MK][MT + 1], Bs[FIRST ? 2 : 1][MK][MT + 1];
+    __shared__ int arow[MT];
+    pdl_launch_dependents();
+    pdl_wait();
+    int e, s0, s1;
+    if (!moe_find_tile(offsets, X, blockIdx.y, &e, &s0, &s1)) return;
+    const int n0 = blockIdx.x * MT, tid = threadIdx.x;
+    if (tid < MT) arow[tid] = s0 + tid < s1 ? (FIRST ? order[s0 + tid] / top : s0 + tid) : -1;
+    __syncthreads();
+    const T *We = W + (size_t)e * (FIRST ? 2 : 1) * N * K;
+    const int tx = tid & 15, ty = tid >> 4;          // outputs n0 + tx + 16 j, slots s0 + ty + 16 i
+    float acc[FIRST ? 2 : 1][4][4] = {};
+    for (int k0 = 0; k0 < K; k0 += MK) {
+        for (int i = tid; i < MT * MK; i += 256) {
+            const int r = i / MK, k = i % MK;
+            const int ar = arow[r];
+            As[k][r] = (ar >= 0 && k0 + k < K) ? to_f32<T>(A[(size_t)ar * lda + k0 + k]) : 0.f;
+            const bool ok = n0 + r < N && k0 + k < K;
+            Bs[0][k][r] = ok ? to_f32<T>(We[(size_t)(n0 + r) * K + k0 + k]) : 0.f;
+            if (FIRST) Bs[FIRST ? 1 : 0][k][r] = ok ? to_f32<T>(We[(size_t)(N + n0 + r) * K + k0 + k]) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < MK; k++) {
+            float a[4], b[4], b2[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) a[i] = As[k][ty + 16 * i];
+#pragma unroll
+            for (int j = 0; j < 4; j++) { b[j] = Bs[0][k][tx + 16 * j]; b2[j] = FIRST ? Bs[FIRST ? 1 : 0][k][tx + 16 * j] : 0.f; }
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    acc[0][i][j] = fmaf(a[i], b[j], acc[0][i][j]);
+                    if (FIRST) acc[FIRST ? 1 : 0][i][j] = fmaf(a[i], b2[j], acc[FIRST ? 1 : 0][i][j]);
+                }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const int slot = s0 + ty + 16 * i;
+        if (slot >= s1) continue;
+        const float w = FIRST ? pair_weight[order[slot]] : 1.0f;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int n = n0 + tx + 16 * j;
+            if (n >= N) continue;
+            if (FIRST) ((T *)out)[(size_t)slot * ldo + n] = from_f32<T>(expert_act(w * acc[0][i][j], w * acc[FIRST ? 1 : 0][i][j], limit, alpha));
+            else ((float *)out)[(size_t)slot * ldo + n] = acc[0][i][j];
+        }
+    }
+}
+
+// ------------------------------------------------------------------ a few rows (decode): a warp per output, weights streamed once per pair
+template <typename T, bool FIRST>
+__global__ void __launch_bounds__(256)
+moe_rows_kernel(const T *__restrict__ A, int lda, const T *__restrict__ W, void *__restrict__ out, int ldo,
+                const int *__restrict__ pair_expert, const int *__restrict__ order, const float *__restrict__ pair_weight, int top,
+                int N, int K, float limit, float alpha) {
+    extern __shared__ float xs[];                    // [K] the slot's input row
+    pdl_launch_dependents();
+    pdl_wait();
+    const int slot = blockIdx.y, pair = order[slot], e = pair_expert[pair];
+    const T *a = A + (size_t)(FIRST ? pair / top : slot) * lda;
+    for (int k = threadIdx.x; k < K; k += 256) xs[k] = to_f32<T>(a[k]);
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const T *We = W + (size_t)e * (FIRST ? 2 : 1) * N * K;
+    const float w = FIRST ? pair_weight[pair] : 1.0f;
+    for (int n = blockIdx.x * 8 + warp; n < N; n += gridDim.x * 8) {
+        const T *g = We + (size_t)n * K, *u = We + (size_t)(N + n) * K;
+        float sg = 0.f, su = 0.f;
+        for (int k = lane; k < K; k += 32) {
+            sg = fmaf(xs[k], to_f32<T>(g[k]), sg);
+            if (FIRST) su = fmaf(xs[k], to_f32<T>(u[k]), su);
+        }
+        sg = warp_sum(sg);
+        if (FIRST) su = warp_sum(su);
+        if (lane == 0) {
+            if (FIRST) ((T *)out)[(size_t)slot * ldo + n] = from_f32<T>(expert_act(w * sg, w * su, limit, alpha));
+            else ((float *)out)[(size_t)slot * ldo + n] = sg;
+        }
+    }
+}
+
+// y: [M * top, F] in T.  x: [M, E].  w_in: [X, 2F, E].
+extern "C" int fg_moe_first(const void *x, int ldx, const void *w_in, void *y, int ldy, int dtype, const int *pair_expert,
+                            const int *offsets, const int *order, const float *pair_weight, int M, int X, int top, int F, int E,
+                            float limit, float alpha, cudaStream_t stream) {
+    if (M <= 0) return 0;
+    const int P = M * top;
+    if (dtype != FG_F32 && dtype != FG_BF16) return FG_ERR_BAD_DTYPE;
+    if (P <= 16 && (size_t)E * 4 <= 48 * 1024) {
+        dim3 grid((F + 7) / 8 < 128 ? (F + 7) / 8 : 128, P);
+        if (dtype == FG_F32)
+            return fg_launch(moe_rows_kernel<float, true>, grid, dim3(256), (size_t)E * 4, stream, (const float *)x, ldx, (const float *)w_in,
+                             y, ldy, pair_expert, order, pair_weight, top, F, E, limit, alpha);
+        return fg_launch(moe_rows_kernel<bf16, true>, grid, dim3(256), (size_t)E * 4, stream, (const bf16 *)x, ldx, (const bf16 *)w_in, y, ldy,
+                         pair_expert, order, pair_weight, top, F, E, limit, alpha);
+    }
+    dim3 grid((F + MT - 1) / MT, (P + MT - 1) / MT + X);
+    if (grid.y > 65535) return FG_ERR_BAD_SIZE;
+    if (dtype == FG_F32)
+        return fg_launch(moe_tile_kernel<float, true>, grid, dim3(256), 0, stream, (const float *)x, ldx, (const float *)w_in, y, ldy, offsets,
+                         order, pair_weight, X, top, F, E, limit, alpha);
+    return fg_launch(moe_tile_kernel<bf16, true>, grid, dim3(256), 0, stream, (const bf16 *)x, ldx, (const bf16 *)w_in, y, ldy, offsets, order,
+                     pair_weight, X, top, F, E, limit, alpha);
+}
+
+// out: [M * top, E] float32.  y: [M * top, F].  w_out: [X, E, F].
+extern "C" int fg_moe_second(const void *y, int ldy, const void *w_out, float *out, int ldo, int dtype, const int *pair_expert,
+                             const int *offsets, const int *order, int M, int X, int top, int F, int E, cudaStream_t stream) {
+    if (M <= 0) return 0;
+    const int P = M * top;
+    if (dtype != FG_F32 && dtype != FG_BF16) return FG_ERR_BAD_DTYPE;
+    if (P <= 16 && (size_t)F * 4 <= 48 * 1024) {
+        dim3 grid((E + 7) / 8 < 128 ? (E + 7) / 8 : 128, P);
+        if (dtype == FG_F32)
+            return fg_launch(moe_rows_kernel<float, false>, grid, dim3(256), (size_t)F * 4, stream, (const float *)y, ldy, (const float *)w_out,
+                             (void *)out, ldo, pair_expert, order, (const float *)nullptr, top, E, F, 0.f, 0.f);
+        return fg_launch(moe_rows_kernel<bf16, false>, grid, dim3(256), (size_t)F * 4, stream, (const bf16 *)y, ldy, (const bf16 *)w_out,
+                         (void *)out, ldo, pair_expert, order, (const float *)nullptr, top, E, F, 0.f, 0.f);
+    }
+    dim3 grid((E + MT - 1) / MT, (P + MT - 1) / MT + X);
+    if (grid.y > 65535) return FG_ERR_BAD_SIZE;
+    if (dtype == FG_F32)
+        return fg_launch(moe_tile_kernel<float, false>, grid, dim3(256), 0, stream, (const float *)y, ldy, (const float *)w_out, (void *)out,
+                         ldo, offsets, order, (const float *)nullptr, X, top, E, F, 0.f, 0.f);
+    return fg_launch(moe_tile_kernel<bf16, false>, grid, dim3(256), 0, stream, (const bf16 *)y, ldy, (const bf16 *)w_out, (void *)out, ldo,
+                     offsets, order, (const float *)nullptr, X, top, E, F, 0.f, 0.f);
+}
+
+// ------------------------------------------------------------------ sum of a row's experts, in the order of its choices
+__global__ void moe_combine_kernel(const float *__restrict__ slot_out, int ld, const int *__restrict__ slot_of, float *__restrict__ t,
+                                   int top, int E, int accumulate) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int r = blockIdx.x;
+    for (int i = threadIdx.x; i < E; i += blockDim.x) {
+        float s = 0.f;
+        for (int k = 0; k < top; k++) s += slot_out[(size_t)slot_of[r * top + k] * ld + i];
+        if (accumulate) t[(size_t)r * E + i] += s;
+        else t[(size_t)r * E + i] = s;
+    }
+}
+
+extern "C" int fg_moe_combine(const float *slot_out, int ld, const int *slot_of, float *t, int M, int top, int E, int accumulate,
+                              cudaStream_t stream) {
+    if (M <= 0) return 0;
+    return fg_launch(moe_combine_kernel, dim3(M), dim3(E >= 1024 ? 256 : 128), 0, stream, slot_out, ld, slot_of, t, top, E, accumulate);
+}

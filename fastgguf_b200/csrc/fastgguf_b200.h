@@ -3,7 +3,7 @@
  * Every function launches on `stream` and returns 0, a cudaError_t, or one of the FG_ERR_* codes
  * below; none allocates device memory.  Pointers are device pointers unless said otherwise.
  * dtype codes: FG_F32 = 0, FG_BF16 = 1.  Page pools are [pages, kv_heads, page, head_dim]; block
- * tables are [sequences, table_width] int32 page ids.  The Python package calls these through ctypes
+ * tables are [sequences, table_width] int32 page ids (a value pool has head size hdv where a function names one).  The Python package calls these through ctypes
  * (fastgguf_b200/ops); the formulas each one follows are cited in its .cu file.
  */
 #pragma once
@@ -29,6 +29,15 @@ int fg_rmsnorm(const float *x, const float *w, const int *rows, void *out, int o
 int fg_rope_append(void *qkv, int dtype, int ld, const int *positions, const int *row_seq, const int *block_table,
                    int table_width, void *k_pool, void *v_pool, const float *cos_t, const float *sin_t, int M, int H,
                    int KV, int hd, int page_size, int write_kv, cudaStream_t stream);
+/* keys [KV, hd] and values [KV, hdv] of each row to their pages, unrotated; k_off: where the keys start in a row */
+int fg_kv_append(const void *qkv, int dtype, int ld, int k_off, const int *positions, const int *row_seq,
+                 const int *block_table, int table_width, void *k_pool, void *v_pool, int M, int KV, int hd, int hdv,
+                 int page_size, cudaStream_t stream);
+/* x += t / rms(t) * w_post; with w_next also out = x / rms(x) * w_next (out_dtype) */
+int fg_norm_add_norm(const float *t, const float *w_post, float *x, const float *w_next, void *out, int out_dtype,
+                     int M, int E, float eps_post, float eps_next, cudaStream_t stream);
+int fg_activation(void *z, int dtype, long long total, int kind /* 0: relu(z)^2 */, cudaStream_t stream);
+int fg_softcap(float *logits, int R, int V, int ld, float cap, cudaStream_t stream);
 int fg_silu_mul(const void *gu, void *out, int dtype, int M, int F, cudaStream_t stream);
 int fg_decode_advance(int *tokens, int *positions, const int *next_tokens, const int *active, int B, cudaStream_t stream);
 int fg_gemm_generic(const void *A, int a_dtype, int lda, const void *W, int w_dtype, int ldw, void *C, int out_dtype,
@@ -37,11 +46,37 @@ int fg_attention_generic(const void *q, int ldq, void *out, int ldo, int dtype, 
                          const int *row_seq, const int *block_table, int table_width, const void *k_pool,
                          const void *v_pool, int M, int H, int KV, int hd, int page_size, float scale, int window,
                          cudaStream_t stream);
+/* the same with values of head size hdv and, with a window, the sequence's first keep_first keys visible as well */
+int fg_attention_generic_kept(const void *q, int ldq, void *out, int ldo, int dtype, const int *positions,
+                              const int *row_seq, const int *block_table, int table_width, const void *k_pool,
+                              const void *v_pool, int M, int H, int KV, int hd, int hdv, int page_size, float scale,
+                              int window, int keep_first, cudaStream_t stream);
 int fg_sample(float *logits, int B, int V, int ldl, float temp, int top_k, float top_p, float repeat_penalty,
               int repeat_last_n, const int *seq_slot, unsigned long long *rng, int *hist, int hist_cap,
               int *hist_count, const int *stop_ids, int n_stop, int *out_tokens,
               unsigned long long *scratch /* [B, 4096] or null */, cudaStream_t stream);
 int fg_argmax(const float *logits, int B, int V, int ldl, int *out, cudaStream_t stream);
+
+/* ---- libfg_mix: retention (linear attention with a fixed decay per head) and the mixture of experts */
+/* proj rows: q [H, dk] | k [H, dk] | v [H, dv] | g [H, dv] float32; state [slots, H, dk, dv] float32; out [M, H * dv] */
+int fg_retention(const float *proj, int ld, void *out, int out_dtype, int ldo, const int *positions, const int *cu_rows,
+                 const int *slots, const float *cos_t, const float *sin_t, const float *decay, float *state, int n_seq,
+                 int H, int dk, int dv, float k_scale, float eps, cudaStream_t stream);
+int fg_retention_chunk_tokens(void);
+int fg_retention_chunked_ok(int dk, int dv);
+int fg_retention_chunked(const float *proj, int ld, void *out, int out_dtype, int ldo, const int *positions,
+                         const int *cu_rows, const int *slots, const float *cos_t, const float *sin_t,
+                         const float *decay, float *state, int *plan, float *U, int n_seq, int n_chunks, int H, int dk,
+                         int dv, float k_scale, float eps, cudaStream_t stream);
+int fg_moe_route(const float *logits, int M, int X, int top, int *pair_expert, float *pair_weight, int *offsets, int *order,
+                 int *slot_of, cudaStream_t stream);
+int fg_moe_first(const void *x, int ldx, const void *w_in, void *y, int ldy, int dtype, const int *pair_expert,
+                 const int *offsets, const int *order, const float *pair_weight, int M, int X, int top, int F, int E,
+                 float limit, float alpha, cudaStream_t stream);
+int fg_moe_second(const void *y, int ldy, const void *w_out, float *out, int ldo, int dtype, const int *pair_expert,
+                  const int *offsets, const int *order, int M, int X, int top, int F, int E, cudaStream_t stream);
+int fg_moe_combine(const float *slot_out, int ld, const int *slot_of, float *t, int M, int top, int E, int accumulate,
+                   cudaStream_t stream);
 
 /* ---- libfg_tc: bf16 contraction on tcgen05 / TMA / tensor memory */
 int fg_gemm_tc(const void *X, int ldx, const void *W, int ldw, void *out, int ldc, int epi, int M, int N, int K,

@@ -10,7 +10,9 @@
  *   {"hidden_size": E, "vocab_size": V, "max_positions": N,
  *    "embedding":  PART, "final_norm": PART, "head": PART,
  *    "layers":   [{"block": "prenorm", "mixer": PART, "feed_forward": PART, "mixer_norm": PART,
- *                  "feed_forward_norm": PART}, ...],
+ *                  "feed_forward_norm": PART}, ...],            "feed_forward": null: a layer without one (then
+ *                                                               no feed_forward_norm either); optional
+ *                                                               "mixer_post_norm", "feed_forward_post_norm": PART
  *    "schedule": [{"layer": 0, "cache_from": null}, ...],      the order in which layers run: an entry may
  *                                                               name a layer twice (a cache of its own each
  *                                                               time) or read an EARLIER entry's cache
@@ -20,15 +22,24 @@
  *   of an attention mixer); nested parts with equal kind and parameters are built once and shared.
  *
  * Built-in kinds
- *   norm          "rmsnorm"        {size, eps}
+ *   norm          "rmsnorm"        {size, eps, offset: 0.0}     y = x / rms(x) * (offset + w)
  *   position      "rope"           {head_dim, theta, scaling: null | {rope_type: "llama3", ...},
  *                                   rotary_dim: head_dim, layout: "halves" | "adjacent"}
  *   mixer         "gqa_attention"  {hidden_size, n_heads, n_kv_heads, head_dim, position: PART | null,
- *                                   scale: null = 1/sqrt(head_dim), window: null}
+ *                                   scale: null = 1/sqrt(head_dim), window: null, keep_first: 0,
+ *                                   v_head_dim: head_dim}        tensors q/k/v/o_proj.weight
+ *                 "retention"      {hidden_size, n_heads, head_dim, v_head_dim, decay: [per head], position: PART | null,
+ *                                   k_scale: null = 1/sqrt(head_dim), eps}   linear attention with a fixed decay per
+ *                                   head, state [heads, head_dim, v_head_dim] float32 per sequence; tensors
+ *                                   q/k/v/g/o_proj.weight
  *   feed_forward  "swiglu"         {hidden_size, d_ff}
+ *                 "mlp"            {hidden_size, d_ff, activation: "relu2"}   down(act(up x))
+ *                 "moe"            {hidden_size, d_ff, n_experts, top_k, limit, alpha: 1.702, router: "sigmoid_input"}
+ *                                   tensors router.weight, experts.<e>.gate/up/down_proj.weight
  *   block         "prenorm"        x += mixer(norm1(x)); x += feed_forward(norm2(x))
+ *                 "sandwich"       x += post1(mixer(norm1(x))); x += post2(feed_forward(norm2(x)))
  *   embedding     "embedding"      {vocab_size, hidden_size, scale: 1.0}
- *   head          "lm_head"        {vocab_size, hidden_size}
+ *   head          "lm_head"        {vocab_size, hidden_size, softcap: null}   logits <- cap tanh(logits / cap)
  *
  * What a part may rely on in fg_batch_view: every device array, and the host integers n_seq, n_rows,
  * n_want, max_new, max_len, single_token, want_all, table_width.  The three host_* arrays are NULL when the
@@ -96,6 +107,7 @@ typedef struct fg_layer_io {
     void *state;             /* [n_slots + 1, state_bytes] fixed-size state of this entry, or NULL */
     int64_t state_bytes;
     int n_slots;
+    int v_head_dim;          /* v_pool is [n_pages, n_kv_heads, page_size, v_head_dim]; equal to head_dim unless asked otherwise */
 } fg_layer_io;
 
 struct fg_part_call;
@@ -132,7 +144,8 @@ typedef struct fg_part_vtable {
     int (*tensor_decl)(void *self, int i, fg_tensor_decl *out);
     /* Tensor i on the device (engine dtype policy applied); it lives as long as the engine. */
     int (*load)(void *self, int i, const fg_dev_tensor *t);
-    /* mixer: 1 and the three numbers if it keeps keys and values per position (window 0 = all of them) */
+    /* mixer: 1 and the three numbers if it keeps keys and values per position (window 0 = all of them); values
+     * have the keys' head size */
     int (*cache_request)(void *self, int *n_kv_heads, int *head_dim, int *window);
     /* mixer: bytes of fixed-size state per sequence (zeroed when a sequence takes its slot); 0 = none */
     int64_t (*state_bytes)(void *self);

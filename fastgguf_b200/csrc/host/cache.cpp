@@ -50,22 +50,25 @@ PagedKVCache::~PagedKVCache() {
     if (storage_) cudaFree(storage_);
 }
 
-static int64_t pool_elems(const CacheGroup &g, int page_size) {
-    return (int64_t)g.n_pages * g.request.n_kv_heads * page_size * g.request.head_dim;
+static int64_t pool_elems(const CacheGroup &g, int page_size, bool values) {
+    return (int64_t)g.n_pages * g.request.n_kv_heads * page_size * (values ? g.request.value_dim() : g.request.head_dim);
+}
+static int64_t pool_bytes_of(const CacheGroup &g, int page_size, int dtype, bool values) {
+    return (pool_elems(g, page_size, values) * elem_size(dtype) + 255) / 256 * 256;
 }
 
 int64_t PagedKVCache::pool_bytes(int dtype) const {
     int64_t total = 0;
     for (auto &g : groups) {
-        int64_t one = (pool_elems(g, page_size) * elem_size(dtype) + 255) / 256 * 256;
-        total += 2 * one * (int64_t)g.entries.size();
+        total += (pool_bytes_of(g, page_size, dtype, false) + pool_bytes_of(g, page_size, dtype, true)) * (int64_t)g.entries.size();
     }
     return total;
 }
 
 int64_t PagedKVCache::bytes_per_token(int dtype) const {
     int64_t b = 0;
-    for (auto &g : groups) b += 2LL * g.request.n_kv_heads * g.request.head_dim * elem_size(dtype) * (int64_t)g.entries.size();
+    for (auto &g : groups)
+        b += (int64_t)g.request.n_kv_heads * (g.request.head_dim + g.request.value_dim()) * elem_size(dtype) * (int64_t)g.entries.size();
     return b;
 }
 
@@ -91,10 +94,9 @@ void PagedKVCache::allocate(int dtype) {
     FG_CUDA(cudaMemset(storage_, 0, (size_t)need));
     char *p = (char *)storage_;
     for (auto &g : groups) {
-        int64_t one = (pool_elems(g, page_size) * elem_size(dtype) + 255) / 256 * 256;
         for (int entry : g.entries) {
-            g.k_pools[entry] = p; p += one;
-            g.v_pools[entry] = p; p += one;
+            g.k_pools[entry] = p; p += pool_bytes_of(g, page_size, dtype, false);
+            g.v_pools[entry] = p; p += pool_bytes_of(g, page_size, dtype, true);
         }
     }
 }
@@ -149,6 +151,12 @@ int PagedKVCache::first_needed_page(const CacheGroup &g, int new_length) const {
     return std::max(0, new_length - g.request.window) / page_size;
 }
 
+// Pages at the start of a sequence that a windowed group never gives back: those of its first keep_first positions.
+int PagedKVCache::kept_pages(const CacheGroup &g) const {
+    if (g.request.window <= 0 || g.request.keep_first <= 0) return 0;
+    return (g.request.keep_first + page_size - 1) / page_size;
+}
+
 std::vector<int> PagedKVCache::pages_needed(int s, int n_new) const {
     const Slot &sl = slot(s);
     std::vector<int> out;
@@ -200,8 +208,9 @@ void PagedKVCache::commit(const std::vector<std::pair<int, int>> &steps) {
         sl.length += st.second;
         for (size_t gi = 0; gi < groups.size(); gi++) {
             if (groups[gi].request.window <= 0) continue;
-            int keep_from = first_needed_page(groups[gi], sl.length);
+            int keep_from = first_needed_page(groups[gi], sl.length), kept = kept_pages(groups[gi]);
             for (auto it = sl.pages[gi].begin(); it != sl.pages[gi].end() && it->first < keep_from;) {
+                if (it->first < kept) { ++it; continue; }
                 groups[gi].free.push_back(it->second);
                 it = sl.pages[gi].erase(it);
             }
@@ -260,6 +269,8 @@ Json PagedKVCache::info() const {
         o.set("n_kv_heads", g.request.n_kv_heads);
         o.set("head_dim", g.request.head_dim);
         o.set("window", g.request.window > 0 ? Json(g.request.window) : Json());
+        o.set("v_head_dim", g.request.value_dim());
+        o.set("keep_first", g.request.window > 0 ? g.request.keep_first : 0);
         Json es = Json::array();
         for (int e : g.entries) es.push(Json(e));
         o.set("entries", es);
@@ -324,6 +335,8 @@ std::map<int, CacheRequest> cache_requests_from_json(const Json &j) {
         c.n_kv_heads = (int)r.get("n_kv_heads").as_int();
         c.head_dim = (int)r.get("head_dim").as_int();
         c.window = r.get("window").is_int() ? (int)r.get("window").as_int() : 0;
+        c.v_head_dim = r.get("v_head_dim").is_int() ? (int)r.get("v_head_dim").as_int() : 0;
+        c.keep_first = r.get("keep_first").is_int() ? (int)r.get("keep_first").as_int() : 0;
         out[(int)r.get("entry").as_int()] = c;
     }
     return out;

@@ -12,7 +12,9 @@
 //   * a cache group is the set of schedule entries whose mixers asked for the same (KV heads, head size,
 //     window); it has storage of its own - one pool per entry, [pages, kv_heads, page_size, head_dim] -
 //     and one page table per sequence, so a full-attention group and a windowed group never share pages;
-//   * a windowed group gives pages back as soon as every position in them has left the window;
+//   * a windowed group gives pages back as soon as every position in them has left the window, except the pages
+//     of the sequence's first keep_first positions when its mixers go on reading those;
+//   * keys and values may have different head sizes (v_head_dim);
 //   * page 0 of every group is never handed out: padded rows of a fixed-shape step write there;
 //   * StatePool keeps [n_slots + 1, bytes] per schedule entry that asked for fixed-size state; a slot's
 //     rows are zeroed when a sequence takes the slot, and the last row is a spare for padded rows.
@@ -33,8 +35,21 @@ namespace fg {
 struct CacheRequest {
     int n_kv_heads = 0, head_dim = 0;
     int window = 0;                           // 0 keeps every position; w keeps the last w
+    int v_head_dim = 0;                       // size of a value head; 0 = head_dim
+    int keep_first = 0;                       // with a window: the first positions of a sequence that stay readable
+    int value_dim() const { return v_head_dim > 0 ? v_head_dim : head_dim; }
     bool operator==(const CacheRequest &o) const {
-        return n_kv_heads == o.n_kv_heads && head_dim == o.head_dim && window == o.window;
+        return n_kv_heads == o.n_kv_heads && head_dim == o.head_dim && window == o.window && value_dim() == o.value_dim() &&
+               (window > 0 ? keep_first : 0) == (o.window > 0 ? o.keep_first : 0);
+    }
+    // the same storage: what a run that reads another run's cache must agree on with its owner
+    bool same_storage(const CacheRequest &o) const {
+        return n_kv_heads == o.n_kv_heads && head_dim == o.head_dim && value_dim() == o.value_dim();
+    }
+    // keep whatever `o` reads as well (a reader with another window or other kept positions)
+    void widen(const CacheRequest &o) {
+        window = (window <= 0 || o.window <= 0) ? 0 : (window > o.window ? window : o.window);
+        keep_first = keep_first > o.keep_first ? keep_first : o.keep_first;
     }
 };
 
@@ -89,6 +104,7 @@ private:
     Slot &slot(int s);
     const Slot &slot(int s) const;
     int first_needed_page(const CacheGroup &g, int new_length) const;
+    int kept_pages(const CacheGroup &g) const;
     std::vector<Slot> slots_;
     std::vector<int> free_slots_;
     void *storage_ = nullptr;

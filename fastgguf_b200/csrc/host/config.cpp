@@ -154,9 +154,21 @@ Json merge_generation_config(const std::string &model_dir, const Json &d) {
 
 // ------------------------------------------------------------------------------------ registry
 static std::mutex g_registry_mutex;
+std::unique_ptr<ModelConfig> zirivik_config_from_json(const Json &d);        // config_zirivik.cpp
 static std::map<std::string, ConfigReader> &registry() {
-    static std::map<std::string, ConfigReader> r = {{"LlamaForCausalLM", &LlamaConfig::from_json}};
+    static std::map<std::string, ConfigReader> r = {{"LlamaForCausalLM", &LlamaConfig::from_json}, {"Zirivik", &zirivik_config_from_json}};
     return r;
+}
+
+// The architecture's name: "architectures": [name, ...] as model folders of the hub write it, or "architecture": name.
+static std::string architecture_of(const Json &d) {
+    if (d.is_object()) {
+        const Json &archs = d.get("architectures");
+        if (archs.is_array() && archs.size() > 0 && archs[0].is_string()) return archs[0].as_string();
+        const Json &one = d.get("architecture");
+        if (archs.is_null() && one.is_string()) return one.as_string();
+    }
+    fail(FG_E_CONFIG, "config.json: 'architectures' must be a non-empty list of names (or 'architecture' a name)");
 }
 
 void register_architecture(const std::string &name, ConfigReader reader) {
@@ -172,19 +184,17 @@ std::vector<std::string> registered_architectures() {
 }
 
 std::unique_ptr<ModelConfig> config_from_json(const Json &d) {
-    const Json &archs = d.get("architectures");
-    if (!d.is_object() || !archs.is_array() || archs.size() == 0 || !archs[0].is_string())
-        fail(FG_E_CONFIG, "config.json: 'architectures' must be a non-empty list of names");
+    const std::string name = architecture_of(d);
     ConfigReader reader;
     {
         std::lock_guard<std::mutex> lock(g_registry_mutex);
-        auto it = registry().find(archs[0].as_string());
+        auto it = registry().find(name);
         if (it != registry().end()) reader = it->second;
     }
     if (!reader) {
         std::string known;
         for (auto &n : registered_architectures()) known += (known.empty() ? "" : ", ") + n;
-        fail(FG_E_CONFIG, "architecture '" + archs[0].as_string() + "' is not registered (registered: " +
+        fail(FG_E_CONFIG, "architecture '" + name + "' is not registered (registered: " +
                               (known.empty() ? "none" : known) + ")");
     }
     return reader(d);

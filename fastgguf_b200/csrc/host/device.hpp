@@ -121,5 +121,6 @@ void dev_convert(const void *src, int src_dtype, void *dst, int dst_dtype, int64
 void dev_gather_rows(const void *src, void *dst, const std::vector<int64_t> &rows, int64_t cols, int dtype, cudaStream_t s);
 void dev_fill_random(void *dst, int dtype, int64_t n, uint64_t seed, uint64_t name_hash, int init, float std, cudaStream_t s);
 void dev_scale_f32(float *x, int64_t n, float scale, cudaStream_t s);
+void dev_shift_f32(float *x, int64_t n, float add, cudaStream_t s);
 
 }  // namespace fg

@@ -111,4 +111,14 @@ void dev_scale_f32(float *x, int64_t n, float scale, cudaStream_t s) {
     FG_CUDA(cudaGetLastError());
 }
 
+__global__ void shift_f32_kernel(float *x, int64_t n, float add) {
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) x[i] += add;
+}
+
+void dev_shift_f32(float *x, int64_t n, float add, cudaStream_t s) {
+    if (n <= 0) return;
+    shift_f32_kernel<<<grid_for(n), 256, 0, s>>>(x, n, add);
+    FG_CUDA(cudaGetLastError());
+}
+
 }  // namespace fg

@@ -41,9 +41,15 @@ ModelSpec ModelSpec::from_json(const Json &j) {
         if (!l.is_object() || !l.get("block").is_string()) fail(FG_E_CONFIG, "model spec: a layer needs a 'block' kind");
         ls.block = l.get("block").as_string();
         ls.mixer = part_spec_from_json(l.get("mixer"), "mixer");
-        ls.feed_forward = part_spec_from_json(l.get("feed_forward"), "feed_forward");
         ls.mixer_norm = part_spec_from_json(l.get("mixer_norm"), "mixer_norm");
-        ls.feed_forward_norm = part_spec_from_json(l.get("feed_forward_norm"), "feed_forward_norm");
+        if (!l.get("feed_forward").is_null()) {                       // null or absent: a layer of a mixer alone
+            ls.feed_forward = part_spec_from_json(l.get("feed_forward"), "feed_forward");
+            ls.feed_forward_norm = part_spec_from_json(l.get("feed_forward_norm"), "feed_forward_norm");
+        } else if (!l.get("feed_forward_norm").is_null() || !l.get("feed_forward_post_norm").is_null())
+            fail(FG_E_CONFIG, "model spec: a layer without a feed-forward has no norms for one");
+        if (!l.get("mixer_post_norm").is_null()) ls.mixer_post_norm = part_spec_from_json(l.get("mixer_post_norm"), "mixer_post_norm");
+        if (!l.get("feed_forward_post_norm").is_null())
+            ls.feed_forward_post_norm = part_spec_from_json(l.get("feed_forward_post_norm"), "feed_forward_post_norm");
         s.layers.push_back(std::move(ls));
     }
     for (auto &r : j.get("schedule").items()) {
@@ -91,11 +97,21 @@ DecoderModel::DecoderModel(const ModelSpec &spec_, int dtype, int device, cudaSt
     embedding_ = dynamic_cast<Embedding *>(build(FG_ROLE_EMBEDDING, spec.embedding));
     for (auto &layer : spec.layers) {
         Mixer *mixer = dynamic_cast<Mixer *>(build(FG_ROLE_MIXER, layer.mixer));
-        FeedForward *ffn = dynamic_cast<FeedForward *>(build(FG_ROLE_FEED_FORWARD, layer.feed_forward));
         Norm *n1 = dynamic_cast<Norm *>(build(FG_ROLE_NORM, layer.mixer_norm));
-        Norm *n2 = dynamic_cast<Norm *>(build(FG_ROLE_NORM, layer.feed_forward_norm));
+        FeedForward *ffn = nullptr;
+        Norm *n2 = nullptr, *p1 = nullptr, *p2 = nullptr;
+        if (layer.has_feed_forward()) {
+            ffn = dynamic_cast<FeedForward *>(build(FG_ROLE_FEED_FORWARD, layer.feed_forward));
+            n2 = dynamic_cast<Norm *>(build(FG_ROLE_NORM, layer.feed_forward_norm));
+            if (!ffn || !n2) fail(FG_E_INTERNAL, "a part was registered under the wrong role");
+        }
+        if (!layer.mixer_post_norm.kind.empty()) p1 = dynamic_cast<Norm *>(build(FG_ROLE_NORM, layer.mixer_post_norm));
+        if (!layer.feed_forward_post_norm.kind.empty()) p2 = dynamic_cast<Norm *>(build(FG_ROLE_NORM, layer.feed_forward_post_norm));
+        if (!mixer || !n1) fail(FG_E_INTERNAL, "a part was registered under the wrong role");
         std::unique_ptr<Block> b = build_block(layer.block, runtime);
         b->mixer = mixer; b->feed_forward = ffn; b->mixer_norm = n1; b->feed_forward_norm = n2;
+        b->mixer_post_norm = p1; b->feed_forward_post_norm = p2;
+        b->check_layer();
         blocks_.push_back(std::move(b));
         mixers_.push_back(mixer);
     }
@@ -269,12 +285,14 @@ void DecoderModel::make_cache(int64_t max_tokens, int n_slots, int max_seq_len, 
         bool wants = m->cache_request(&r);
         if (spec.schedule[i].cache_from < 0 && wants) cache_req[(int)i] = r;
         if (spec.schedule[i].cache_from >= 0) {
-            // a borrowed cache must be of the shape the borrower reads
+            // a borrowed cache must be of the shape the borrower reads; the owner keeps whatever its readers still see
+            // (a reader may have another window or other kept first positions than the owner)
             Mixer *owner = mixers_[(size_t)spec.schedule[(size_t)spec.schedule[i].cache_from].layer];
             CacheRequest ro;
-            if (!wants || !owner->cache_request(&ro) || !(ro == r))
+            if (!wants || !owner->cache_request(&ro) || !ro.same_storage(r))
                 fail(FG_E_CONFIG, format("schedule[%zu] reads the cache of entry %d, whose mixer keeps different keys and values", i,
                                          spec.schedule[i].cache_from));
+            cache_req.at(spec.schedule[i].cache_from).widen(r);
         }
         if (m->state_bytes() > 0) state_req[(int)i] = m->state_bytes();
     }
@@ -307,6 +325,7 @@ void DecoderModel::make_cache(int64_t max_tokens, int n_slots, int max_seq_len, 
             l.n_pages = g.n_pages;
             l.n_kv_heads = g.request.n_kv_heads;
             l.head_dim = g.request.head_dim;
+            l.v_head_dim = g.request.value_dim();
         }
         io.push_back(l);
     }
@@ -435,10 +454,13 @@ Tensor DecoderModel::forward(Runtime &rt, const Batch &batch) {
     // the final norm can be started by the last block when the head takes every row as it is
     Norm *head_norm = (batch.want_all && bf16 && final_norm_->deferrable() && head_->supports_deferred_norm()) ? final_norm_ : nullptr;
     Tensor x = rt.arena->matrix(batch.n_rows, spec.hidden_size, FG_F32);      // the float32 residual stream
-    Norm *first = n ? entry_norm(block_at(0)) : nullptr;
+    Norm *first = (n && !block_at(0)->finished_norms()) ? entry_norm(block_at(0)) : nullptr;
     DeferredNorm pending = embedding_->forward(rt, batch, x, first);
     for (size_t i = 0; i < n; i++) {
         Norm *next = i + 1 < n ? entry_norm(block_at(i + 1)) : head_norm;
+        // blocks that finish the next norm themselves hand it to a block of the same habit only (any dtype)
+        if (block_at(i)->finished_norms()) next = (i + 1 < n && block_at(i + 1)->finished_norms()) ? block_at(i + 1)->mixer_norm : nullptr;
+        else if (i + 1 < n && block_at(i + 1)->finished_norms()) next = nullptr;
         rt.arena->begin_layer((int)i);                 // this entry's temporaries reuse the memory of entry i - 2
         pending = block_at(i)->forward(rt, x, batch, io[i], pending, next);
     }

@@ -30,6 +30,8 @@ struct PartSpec {
 struct LayerSpec {
     std::string block;
     PartSpec mixer, feed_forward, mixer_norm, feed_forward_norm;
+    PartSpec mixer_post_norm, feed_forward_post_norm;    // optional; a part with an empty kind is absent
+    bool has_feed_forward() const { return !feed_forward.kind.empty(); }
 };
 struct RunSpec {
     int layer = 0;

@@ -1,4 +1,5 @@
-// See parts.hpp.  Built-in kinds: rmsnorm, rope, gqa_attention, swiglu, prenorm, embedding, lm_head; and
+// See parts.hpp.  Built-in kinds: rmsnorm, rope, gqa_attention, swiglu, prenorm, sandwich, embedding, lm_head (the
+// retention mixer lives in parts_recurrent.cpp, the plain and the expert feed-forwards in parts_experts.cpp); and
 // the adapter that runs a part registered from outside through fastgguf_parts.h.
 #include "parts.hpp"
 
@@ -64,6 +65,7 @@ fg_layer_io LayerIO::view() const {
     v.group = group; v.k_pool = k_pool; v.v_pool = v_pool; v.n_pages = n_pages; v.page_size = page_size;
     v.n_kv_heads = n_kv_heads; v.head_dim = head_dim; v.cache_dtype = cache_dtype; v.write_cache = write_cache;
     v.state = state; v.state_bytes = state_bytes; v.n_slots = n_slots;
+    v.v_head_dim = v_head_dim > 0 ? v_head_dim : head_dim;
     return v;
 }
 
@@ -101,7 +103,7 @@ Weight gather_rows(const Weight &w, const std::vector<int64_t> &rows, cudaStream
     return out;
 }
 
-static const Weight &tensor_of(const std::map<std::string, Weight> &tensors, const char *name) {
+const Weight &tensor_of(const std::map<std::string, Weight> &tensors, const char *name) {
     auto it = tensors.find(name);
     if (it == tensors.end()) fail(FG_E_INTERNAL, format("a part was not given its tensor '%s'", name));
     return it->second;
@@ -217,16 +219,19 @@ int decode_splits(int n_sm, int n_seq, int n_heads, int n_kv_heads, int table_wi
     return s;
 }
 
-static bool fast_attention_ok(const Runtime &rt, const Tensor &q, const LayerIO &io, int head_dim) {
-    return !rt.plain_kernels && q.dtype == FG_BF16 && io.cache_dtype == FG_BF16 && (head_dim == 64 || head_dim == 128) && io.page_size == 64 &&
-           q.ld % 2 == 0 && ((uintptr_t)q.data % 4) == 0;
+// The tensor-core attention kernels take bfloat16, head size 64 / 128 for keys and values alike, pages of 64, and a
+// plain window; kept first keys and other sizes go to the any-size kernel.
+static bool fast_attention_ok(const Runtime &rt, const Tensor &q, const LayerIO &io, const AttentionShape &a) {
+    return !rt.plain_kernels && q.dtype == FG_BF16 && io.cache_dtype == FG_BF16 && (a.head_dim == 64 || a.head_dim == 128) &&
+           a.v_head_dim == a.head_dim && !(a.window > 0 && a.keep_first > 0) && io.page_size == 64 && q.ld % 2 == 0 &&
+           ((uintptr_t)q.data % 4) == 0;
 }
 
-static Tensor attention(Runtime &rt, const Tensor &q, const Batch &b, const LayerIO &io, int H, int KV, int hd, float scale,
-                        int window) {
+static Tensor attention(Runtime &rt, const Tensor &q, const Batch &b, const LayerIO &io, const AttentionShape &a) {
+    const int H = a.n_heads, KV = a.n_kv_heads, hd = a.head_dim;
     const int *table = b.block_tables.at((size_t)io.group);
-    Tensor out = rt.arena->matrix(q.rows, (int64_t)H * hd, q.dtype);
-    if (fast_attention_ok(rt, q, io, hd)) {
+    Tensor out = rt.arena->matrix(q.rows, (int64_t)H * a.v_head_dim, q.dtype);
+    if (fast_attention_ok(rt, q, io, a)) {
         if (b.single_token) {
             int n_splits = decode_splits(rt.n_sm, b.n_seq, H, KV, b.table_width, hd);
             float *part_o = nullptr, *part_ml = nullptr;
@@ -235,7 +240,7 @@ static Tensor attention(Runtime &rt, const Tensor &q, const Batch &b, const Laye
                 part_ml = (float *)rt.arena->alloc((size_t)b.n_seq * H * n_splits * 2 * sizeof(float));
             }
             FG_LAUNCH("attn", fg_attention_decode, q.data, (int)q.ld, out.data, (int)out.ld, b.positions, table, b.table_width,
-                      io.k_pool, io.v_pool, b.n_seq, H, KV, hd, io.page_size, scale, window, n_splits, part_o, part_ml, rt.stream);
+                      io.k_pool, io.v_pool, b.n_seq, H, KV, hd, io.page_size, a.scale, a.window, n_splits, part_o, part_ml, rt.stream);
             return out;
         }
         // Many new tokens: 128-row tiles on the tcgen05 tensor cores.  A few rows (a sequence fed in short
@@ -243,57 +248,75 @@ static Tensor attention(Runtime &rt, const Tensor &q, const Batch &b, const Laye
         bool tc = b.max_new * (H / KV) >= 64 && q.ld % 8 == 0 && ((uintptr_t)q.data % 16) == 0;
         if (tc)
             FG_LAUNCH("attn", fg_attention_prefill_tc, q.data, (int)q.ld, out.data, (int)out.ld, b.cu_rows, b.seq_start, table,
-                      b.table_width, io.k_pool, io.v_pool, io.n_pages, b.n_seq, b.max_new, H, KV, hd, io.page_size, scale, window,
+                      b.table_width, io.k_pool, io.v_pool, io.n_pages, b.n_seq, b.max_new, H, KV, hd, io.page_size, a.scale, a.window,
                       rt.stream);
         else
             FG_LAUNCH("attn", fg_attention_prefill, q.data, (int)q.ld, out.data, (int)out.ld, b.cu_rows, b.seq_start, table,
-                      b.table_width, io.k_pool, io.v_pool, b.n_seq, b.max_new, H, KV, hd, io.page_size, scale, window, rt.stream);
+                      b.table_width, io.k_pool, io.v_pool, b.n_seq, b.max_new, H, KV, hd, io.page_size, a.scale, a.window, rt.stream);
         return out;
     }
     if (q.dtype != io.cache_dtype) fail(FG_E_INTERNAL, "attention: q and the cache must share a dtype");
-    if (hd > 256) fail(FG_E_KERNEL, format("attention: head_dim %d exceeds 256, the largest the any-size kernel takes", hd));
-    FG_LAUNCH("core", fg_attention_generic, q.data, (int)q.ld, out.data, (int)out.ld, q.dtype, b.positions, b.row_seq, table,
-              b.table_width, io.k_pool, io.v_pool, (int)q.rows, H, KV, hd, io.page_size, scale, window, rt.stream);
+    if (hd > 256 || a.v_head_dim > 256)
+        fail(FG_E_KERNEL, format("attention: head size %d / %d exceeds 256, the largest the any-size kernel takes", hd, a.v_head_dim));
+    FG_LAUNCH("core", fg_attention_generic_kept, q.data, (int)q.ld, out.data, (int)out.ld, q.dtype, b.positions, b.row_seq, table,
+              b.table_width, io.k_pool, io.v_pool, (int)q.rows, H, KV, hd, a.v_head_dim, io.page_size, a.scale, a.window, a.keep_first,
+              rt.stream);
     return out;
 }
 
 Tensor rope_attention(Runtime &rt, const Tensor &qkv, const Batch &b, const LayerIO &io, const float *cos_t, const float *sin_t,
-                      int H, int KV, int hd, float scale, int window) {
+                      const AttentionShape &a) {
+    const int H = a.n_heads, KV = a.n_kv_heads, hd = a.head_dim;
     if (io.group < 0 || !io.k_pool) fail(FG_E_INTERNAL, "attention: the schedule entry has no cache");
+    if (io.head_dim != hd || (io.v_head_dim > 0 ? io.v_head_dim : io.head_dim) != a.v_head_dim || io.n_kv_heads != KV)
+        fail(FG_E_INTERNAL, "attention: the entry's cache has other sizes than its mixer");
     const int *table = b.block_tables.at((size_t)io.group);
     // A decode step in bfloat16 with head size 64 / 128 on the entry's own cache runs as ONE kernel.  It reads
     // positions, the page table and its own pages before waiting for the kernel in front of it; see common.cuh
     // for why that is allowed here and only here.
-    if (io.write_cache && b.single_token && fast_attention_ok(rt, qkv, io, hd) && qkv.ld % 8 == 0 && ((uintptr_t)qkv.data % 16) == 0) {
+    if (io.write_cache && b.single_token && fast_attention_ok(rt, qkv, io, a) && qkv.ld % 8 == 0 && ((uintptr_t)qkv.data % 16) == 0) {
         int n_splits = decode_splits(rt.n_sm, b.n_seq, H, KV, b.table_width, hd);
         if (n_splits == 1 || n_splits == 2 || n_splits == 4 || n_splits == 8) {
             Tensor out = rt.arena->matrix(qkv.rows, (int64_t)H * hd, FG_BF16);
             FG_LAUNCH("attn", fg_attention_decode_fused, qkv.data, (int)qkv.ld, out.data, (int)out.ld, b.positions, table,
-                      b.table_width, io.k_pool, io.v_pool, cos_t, sin_t, b.n_seq, H, KV, hd, io.page_size, scale, window, n_splits,
+                      b.table_width, io.k_pool, io.v_pool, cos_t, sin_t, b.n_seq, H, KV, hd, io.page_size, a.scale, a.window, n_splits,
                       rt.stream);
             return out;
         }
     }
-    FG_LAUNCH("core", fg_rope_append, qkv.data, qkv.dtype, (int)qkv.ld, b.positions, b.row_seq, table, b.table_width,
-              io.write_cache ? io.k_pool : nullptr, io.write_cache ? io.v_pool : nullptr, cos_t, sin_t, (int)qkv.rows, H, KV, hd,
-              io.page_size, io.write_cache ? 1 : 0, rt.stream);
-    return attention(rt, qkv, b, io, H, KV, hd, scale, window);
+    if (!a.rotate) {
+        // nothing to rotate: keys and values go to the cache as they are
+        if (io.write_cache)
+            FG_LAUNCH("core", fg_kv_append, qkv.data, qkv.dtype, (int)qkv.ld, H * hd, b.positions, b.row_seq, table, b.table_width, io.k_pool,
+                      io.v_pool, (int)qkv.rows, KV, hd, a.v_head_dim, io.page_size, rt.stream);
+    } else {
+        if (a.v_head_dim != hd) fail(FG_E_KERNEL, "attention: rotated keys with values of another head size have no kernel");
+        FG_LAUNCH("core", fg_rope_append, qkv.data, qkv.dtype, (int)qkv.ld, b.positions, b.row_seq, table, b.table_width,
+                  io.write_cache ? io.k_pool : nullptr, io.write_cache ? io.v_pool : nullptr, cos_t, sin_t, (int)qkv.rows, H, KV, hd,
+                  io.page_size, io.write_cache ? 1 : 0, rt.stream);
+    }
+    return attention(rt, qkv, b, io, a);
 }
 
 // ------------------------------------------------------------------------------------ RMSNorm
 // y = x * (1 / sqrt(mean(x^2) + eps)) * w; the weight multiplies directly (no +1), in the order x * inv * w
 // (rmsnorm_w, fastgguf.c:3100-3105).  Statistics are 32-bit here (the reference sums in double).
+// offset: checkpoints that store the weight around zero apply (offset + w); the sum is formed once, in float32, when
+// the weights are loaded, so every kernel (and a norm started inside a contraction) reads a plain weight.
 class RMSNorm : public Norm {
 public:
-    RMSNorm(const Json &p) : size_((int)param_int(p, "size", "rmsnorm")), eps_((float)param_float(p, "eps", "rmsnorm")) {
+    RMSNorm(const Json &p)
+        : size_((int)param_int(p, "size", "rmsnorm")), eps_((float)param_float(p, "eps", "rmsnorm")),
+          offset_((float)param_float(p, "offset", 0.0, "rmsnorm")) {
         if (size_ <= 0 || !(eps_ > 0.f)) fail(FG_E_CONFIG, "rmsnorm: size and eps must be positive");
     }
-    std::vector<TensorDecl> tensor_decls() const override { return {{"weight", {size_}, false, 1, 0.01f}}; }
+    std::vector<TensorDecl> tensor_decls() const override { return {{"weight", {size_}, false, offset_ != 0.f ? 0 : 1, offset_ != 0.f ? 0.1f : 0.01f}}; }
     void load(const std::map<std::string, Weight> &tensors, Runtime &rt) override {
         const Weight &w = tensor_of(tensors, "weight");
         // widening bf16 -> f32 is exact; the kernels read the weight as f32
-        if (w.t.dtype == FG_F32) w_ = w;
+        if (w.t.dtype == FG_F32 && offset_ == 0.f) w_ = w;
         else w_ = concat_rows({w}, FG_F32, rt.stream);
+        if (offset_ != 0.f) dev_shift_f32(w_.t.ptr<float>(), w_.t.numel(), offset_, rt.stream);
     }
     Tensor forward(Runtime &rt, const Tensor &x, const int *rows, int n_rows) override {
         int R = rows ? n_rows : (int)x.rows;
@@ -309,7 +332,7 @@ public:
 
 private:
     int size_;
-    float eps_;
+    float eps_, offset_;
     Weight w_;
 };
 
@@ -451,7 +474,9 @@ private:
 // (:4744), each query head h attends with KV head h / (H / KV) (:4781) to positions [start, pos] (:4754-4758),
 // softmax and value sum (attn_rows :3273-3326), output projection added onto the un-normalized input
 // (:4860-4862).  A run that borrows the cache of an earlier entry computes only q and attends to the owner's
-// keys and values (the reference's shared-KV layers, :4745-4751).
+// keys and values (the reference's shared-KV layers, :4745-4751).  window w: a row sees the last w keys (:4754-4758);
+// keep_first n: and, besides, the first n keys of its sequence, at their own places (what "attention sinks" models
+// keep when their window slides on); v_head_dim: values of another size than the keys.
 class GQAAttention : public Mixer {
 public:
     GQAAttention(const Json &p, BuildContext &ctx) {
@@ -465,12 +490,19 @@ public:
         if (hd_ % 2) fail(FG_E_CONFIG, format("gqa_attention: head_dim must be even, got %d", hd_));
         scale_ = (float)param_float(p, "scale", 1.0 / std::sqrt((double)hd_), me);
         window_ = (int)param_int(p, "window", 0, me);
-        if (window_ < 0) fail(FG_E_CONFIG, "gqa_attention: window cannot be negative");
+        keep_first_ = (int)param_int(p, "keep_first", 0, me);
+        hdv_ = (int)param_int(p, "v_head_dim", hd_, me);
+        if (window_ < 0 || keep_first_ < 0) fail(FG_E_CONFIG, "gqa_attention: window and keep_first cannot be negative");
+        if (hdv_ <= 0) fail(FG_E_CONFIG, "gqa_attention: v_head_dim must be positive");
+        const Json &qo = p.get("queries_only");
+        queries_only_ = qo.is_bool() && qo.as_bool();
         const Json &pos = p.get("position");
+        rotate_ = !pos.is_null();
         if (pos.is_null()) {
             own_position_ = std::make_unique<NoPosition>(hd_);
             position_ = own_position_.get();
         } else {
+            if (hdv_ != hd_) fail(FG_E_CONFIG, "gqa_attention: a position encoding needs v_head_dim == head_dim");
             position_ = dynamic_cast<PositionEncoding *>(ctx.nested(FG_ROLE_POSITION, pos));
             if (!position_) fail(FG_E_CONFIG, "gqa_attention: 'position' is not a position encoding");
             if (position_->head_dim() != hd_)
@@ -480,14 +512,32 @@ public:
     }
     std::vector<TensorDecl> tensor_decls() const override {
         int64_t Q = (int64_t)H_ * hd_, D = (int64_t)KV_ * hd_;
-        return {{"q_proj.weight", {Q, E_}}, {"k_proj.weight", {D, E_}}, {"v_proj.weight", {D, E_}}, {"o_proj.weight", {E_, Q}}};
+        if (queries_only_) return {{"q_proj.weight", {Q, E_}}, {"o_proj.weight", {E_, (int64_t)H_ * hdv_}}};
+        return {{"q_proj.weight", {Q, E_}}, {"k_proj.weight", {D, E_}}, {"v_proj.weight", {(int64_t)KV_ * hdv_, E_}},
+                {"o_proj.weight", {E_, (int64_t)H_ * hdv_}}};
     }
     bool cache_request(CacheRequest *out) const override {
         out->n_kv_heads = KV_; out->head_dim = hd_; out->window = window_;
+        out->v_head_dim = hdv_; out->keep_first = window_ > 0 ? keep_first_ : 0;
         return true;
     }
     bool supports_deferred_norm() const override { return true; }
     void load(const std::map<std::string, Weight> &tensors, Runtime &rt) override {
+        o_ = Linear(tensor_of(tensors, "o_proj.weight"));
+        if (queries_only_) {
+            // a layer that only ever runs on another entry's keys and values: its own rows of q, in the order the
+            // owner's keys are stored in
+            Weight q = tensor_of(tensors, "q_proj.weight");
+            const std::vector<int> &perm = position_->permutation();
+            if (!perm.empty()) {
+                std::vector<int64_t> rows;
+                for (int h = 0; h < H_; h++)
+                    for (int i = 0; i < hd_; i++) rows.push_back((int64_t)h * hd_ + perm[(size_t)i]);
+                q = gather_rows(q, rows, rt.stream);
+            }
+            q_only_ = Linear(q);
+            return;
+        }
         Weight q = tensor_of(tensors, "q_proj.weight"), k = tensor_of(tensors, "k_proj.weight");
         const Weight &v = tensor_of(tensors, "v_proj.weight");
         const std::vector<int> &perm = position_->permutation();
@@ -504,21 +554,25 @@ public:
         int dt = (q.t.dtype == k.t.dtype && k.t.dtype == v.t.dtype) ? q.t.dtype : FG_F32;
         qkv_ = Linear(concat_rows({q, k, v}, dt, rt.stream));
         q_only_ = qkv_.rows(0, (int64_t)H_ * hd_);
-        o_ = Linear(tensor_of(tensors, "o_proj.weight"));
     }
     void prepare(Runtime &rt, int max_positions) override { position_->prepare(rt, max_positions); }
     DeferredNorm forward(Runtime &rt, const Tensor &xn, const DeferredNorm *deferred, const Batch &batch, const LayerIO &io,
                          Tensor &residual, Norm *emit_norm) override {
+        if (io.write_cache && queries_only_) fail(FG_E_CONFIG, "gqa_attention: a queries-only mixer must read another entry's cache");
         const Linear &proj = io.write_cache ? qkv_ : q_only_;
         Tensor qkv = proj.forward(rt, xn, deferred, Tensor(), rt.dtype, false, nullptr, nullptr);
-        Tensor attn = rope_attention(rt, qkv, batch, io, position_->cos_table(), position_->sin_table(), H_, KV_, hd_, scale_, window_);
+        AttentionShape shape;
+        shape.n_heads = H_; shape.n_kv_heads = KV_; shape.head_dim = hd_; shape.v_head_dim = hdv_; shape.scale = scale_;
+        shape.window = window_; shape.keep_first = window_ > 0 ? keep_first_ : 0; shape.rotate = rotate_;
+        Tensor attn = rope_attention(rt, qkv, batch, io, position_->cos_table(), position_->sin_table(), shape);
         DeferredNorm started;
         o_.forward(rt, attn, nullptr, residual, FG_F32, true, emit_norm, &started);
         return started;
     }
 
 private:
-    int E_, H_, KV_, hd_, window_;
+    int E_, H_, KV_, hd_, hdv_, window_, keep_first_;
+    bool rotate_ = true, queries_only_ = false;
     float scale_;
     PositionEncoding *position_ = nullptr;
     std::unique_ptr<PositionEncoding> own_position_;
@@ -582,11 +636,23 @@ private:
 // that reads the normalised rows; parts that do not take part get plain normalised tensors.
 class PreNormBlock : public Block {
 public:
+    void check_layer() const override {
+        Block::check_layer();
+        if (mixer_post_norm || feed_forward_post_norm) fail(FG_E_CONFIG, "block 'prenorm' has no norms behind its sublayers (see 'sandwich')");
+    }
     DeferredNorm forward(Runtime &rt, Tensor &x, const Batch &batch, const LayerIO &io, const DeferredNorm &pending,
                          Norm *next_norm) override {
         bool bf16 = rt.dtype == FG_BF16;
-        bool mixer_defers = bf16 && mixer->supports_deferred_norm(), ffn_defers = bf16 && feed_forward->supports_deferred_norm();
+        bool mixer_defers = bf16 && mixer->supports_deferred_norm();
+        bool ffn_defers = bf16 && feed_forward && feed_forward->supports_deferred_norm();
         DeferredNorm started;
+        if (!feed_forward) {
+            // a layer of a mixer alone: its output projection may start the next layer's norm
+            if (mixer_defers && pending.defined()) return mixer->forward(rt, Tensor(), &pending, batch, io, x, next_norm);
+            if (mixer_defers) return mixer->forward(rt, mixer_norm->forward(rt, x, nullptr, 0), nullptr, batch, io, x, next_norm);
+            mixer->forward(rt, mixer_norm->forward(rt, x, nullptr, 0), nullptr, batch, io, x, nullptr);
+            return DeferredNorm();
+        }
         if (mixer_defers) {
             Norm *emit = (ffn_defers && feed_forward_norm->deferrable()) ? feed_forward_norm : nullptr;
             if (pending.defined()) started = mixer->forward(rt, Tensor(), &pending, batch, io, x, emit);
@@ -600,6 +666,62 @@ public:
         }
         feed_forward->forward(rt, feed_forward_norm->forward(rt, x, nullptr, 0), nullptr, batch, x, nullptr);
         return DeferredNorm();
+    }
+};
+
+void Block::check_layer() const {
+    if (!mixer || !mixer_norm) fail(FG_E_CONFIG, "a layer needs a mixer and its norm");
+    if ((feed_forward == nullptr) != (feed_forward_norm == nullptr)) fail(FG_E_CONFIG, "a layer has a feed-forward and its norm, or neither");
+    if (!feed_forward && feed_forward_post_norm) fail(FG_E_CONFIG, "a layer without a feed-forward cannot have a norm behind it");
+}
+
+// ------------------------------------------------------------------------------------ sandwich block
+// x += post1(mixer(norm1(x))); x += post2(feed_forward(norm2(x))): each sublayer's output is normalised before it
+// joins the residual stream.  The sublayer writes its output into a zeroed float32 buffer of the stream's shape (its
+// last projection adds into it as it would into the stream), and ONE kernel then normalises that buffer, adds it to the
+// stream and, where the next reader of the stream is a norm of this block or the next, produces that norm's output as
+// well - so the stream is read and written once per sublayer.  The residual sum and all statistics are 32-bit.
+class SandwichBlock : public Block {
+public:
+    void check_layer() const override {
+        Block::check_layer();
+        if (!mixer_post_norm || (feed_forward && !feed_forward_post_norm))
+            fail(FG_E_CONFIG, "block 'sandwich' needs mixer_post_norm (and feed_forward_post_norm where there is a feed-forward)");
+        for (Norm *n : {mixer_norm, mixer_post_norm, feed_forward_norm, feed_forward_post_norm})
+            if (n && !n->deferrable()) fail(FG_E_CONFIG, "block 'sandwich' takes norms of the form x / rms(x) * w");
+    }
+    bool finished_norms() const override { return true; }
+    // pending.xw (when defined, with tiles == 0) holds the FINISHED norm of x for this block's mixer, made by the block before
+    DeferredNorm forward(Runtime &rt, Tensor &x, const Batch &batch, const LayerIO &io, const DeferredNorm &pending,
+                         Norm *next_norm) override {
+        const int M = (int)x.rows, E = (int)x.cols;
+        Tensor xn = !pending.defined() ? mixer_norm->forward(rt, x, nullptr, 0) : pending.tiles == 0 ? pending.xw : pending.materialize(rt);
+        Tensor t = rt.arena->matrix(M, E, FG_F32);
+        auto zero = [&]() { if (M > 0) FG_CUDA(cudaMemsetAsync(t.data, 0, (size_t)M * E * sizeof(float), rt.stream)); };
+        // the norm that reads x after a sublayer: produced by the kernel that adds the sublayer's output
+        auto join = [&](Norm *post, Norm *reader) -> Tensor {
+            Tensor out;
+            if (reader) out = rt.arena->matrix(M, E, rt.dtype);
+            if (M > 0)
+                FG_LAUNCH("core", fg_norm_add_norm, t.ptr<float>(), post->weight(), x.ptr<float>(), reader ? reader->weight() : nullptr,
+                          out.data, rt.dtype, M, E, post->eps(), reader ? reader->eps() : 0.f, rt.stream);
+            return out;
+        };
+        auto finished = [&](const Tensor &xn_next, Norm *reader) {
+            DeferredNorm d;
+            if (reader && xn_next.defined()) { d.xw = xn_next; d.tiles = 0; d.size = E; d.eps = reader->eps(); d.x = x; d.weight = reader->weight(); }
+            return d;
+        };
+        Norm *hand_over = (next_norm && next_norm->deferrable() && next_norm->weight() && E * sizeof(float) <= 48 * 1024) ? next_norm : nullptr;
+        bool fuse_inner = E * sizeof(float) <= 48 * 1024;
+        zero();
+        mixer->forward(rt, xn, nullptr, batch, io, t, nullptr);
+        if (!feed_forward) return finished(join(mixer_post_norm, hand_over), hand_over);
+        Tensor hn = join(mixer_post_norm, fuse_inner ? feed_forward_norm : nullptr);
+        if (!hn.defined()) hn = feed_forward_norm->forward(rt, x, nullptr, 0);
+        zero();
+        feed_forward->forward(rt, hn, nullptr, batch, t, nullptr);
+        return finished(join(feed_forward_post_norm, hand_over), hand_over);
     }
 };
 
@@ -641,20 +763,28 @@ private:
     Weight w_;
 };
 
+// softcap c: logits <- c * tanh(logits / c), on the float32 logits (the reference's final_softcap, fastgguf.c:4064-4100).
 class LMHead : public Head {
 public:
-    LMHead(const Json &p) : V_(param_int(p, "vocab_size", "lm_head")), E_(param_int(p, "hidden_size", "lm_head")) {
+    LMHead(const Json &p)
+        : V_(param_int(p, "vocab_size", "lm_head")), E_(param_int(p, "hidden_size", "lm_head")),
+          softcap_((float)param_float(p, "softcap", 0.0, "lm_head")) {
         if (V_ <= 0 || E_ <= 0) fail(FG_E_CONFIG, "lm_head: sizes must be positive");
+        if (softcap_ < 0.f) fail(FG_E_CONFIG, "lm_head: softcap must be positive (or absent)");
     }
     std::vector<TensorDecl> tensor_decls() const override { return {{"weight", {V_, E_}}}; }
     void load(const std::map<std::string, Weight> &tensors, Runtime &) override { linear_ = Linear(tensor_of(tensors, "weight")); }
     bool supports_deferred_norm() const override { return true; }
     Tensor forward(Runtime &rt, const Tensor &xn, const DeferredNorm *deferred) override {
-        return linear_.forward(rt, xn, deferred, Tensor(), FG_F32, false, nullptr, nullptr);
+        Tensor logits = linear_.forward(rt, xn, deferred, Tensor(), FG_F32, false, nullptr, nullptr);
+        if (softcap_ > 0.f && logits.rows > 0)
+            FG_LAUNCH("core", fg_softcap, logits.ptr<float>(), (int)logits.rows, (int)logits.cols, (int)logits.ld, softcap_, rt.stream);
+        return logits;
     }
 
 private:
     int64_t V_, E_;
+    float softcap_;
     Linear linear_;
 };
 
@@ -943,12 +1073,15 @@ static std::map<std::string, PartFactory> &factories(int role) {
         r[FG_ROLE_FEED_FORWARD]["swiglu"] = [](Runtime &, const Json &p, BuildContext &) { return std::make_unique<SwiGLU>(p); };
         r[FG_ROLE_EMBEDDING]["embedding"] = [](Runtime &, const Json &p, BuildContext &) { return std::make_unique<TokenEmbedding>(p); };
         r[FG_ROLE_HEAD]["lm_head"] = [](Runtime &, const Json &p, BuildContext &) { return std::make_unique<LMHead>(p); };
+        add_recurrent_kinds(r[FG_ROLE_MIXER]);
+        add_expert_kinds(r[FG_ROLE_FEED_FORWARD]);
     }
     if (role < 0 || role > 6) fail(FG_E_USAGE, format("role %d does not exist", role));
     return r[role];
 }
 static std::map<std::string, BlockFactory> &block_factories() {
-    static std::map<std::string, BlockFactory> r = {{"prenorm", [](Runtime &) { return std::make_unique<PreNormBlock>(); }}};
+    static std::map<std::string, BlockFactory> r = {{"prenorm", [](Runtime &) { return std::make_unique<PreNormBlock>(); }},
+                                                     {"sandwich", [](Runtime &) { return std::make_unique<SandwichBlock>(); }}};
     return r;
 }
 
@@ -995,7 +1128,8 @@ std::unique_ptr<Block> build_block(const std::string &kind, Runtime &rt) {
 }
 
 void register_external_part(int role, const std::string &kind, const fg_part_vtable &vt) {
-    static const char *builtin[] = {"rmsnorm", "rope", "gqa_attention", "swiglu", "prenorm", "embedding", "lm_head"};
+    static const char *builtin[] = {"rmsnorm", "rope", "gqa_attention", "retention", "swiglu", "mlp", "moe", "prenorm", "sandwich",
+                                    "embedding", "lm_head"};
     for (auto b : builtin)
         if (kind == b) fail(FG_E_USAGE, "kind '" + kind + "' is built in and cannot be replaced");
     if (kind.empty()) fail(FG_E_USAGE, "a part kind needs a name");

@@ -70,6 +70,7 @@ struct LayerIO {
     int group = -1;
     void *k_pool = nullptr, *v_pool = nullptr;
     int n_pages = 0, page_size = 64, n_kv_heads = 0, head_dim = 0, cache_dtype = FG_BF16;
+    int v_head_dim = 0;               // size of a value head in v_pool (equal to head_dim unless the mixer asked otherwise)
     bool write_cache = true;          // false: the cache belongs to an earlier entry
     void *state = nullptr;
     int64_t state_bytes = 0;
@@ -140,13 +141,20 @@ public:
                                  Tensor &residual, Norm *emit_norm) = 0;
 };
 
-// An arrangement of a mixer, a feed-forward and their norms around the residual stream.
+// An arrangement of a mixer, a feed-forward and their norms around the residual stream.  A layer may have no
+// feed-forward (feed_forward and its norms are then null); the post norms exist only in layers that give them.
 class Block {
 public:
     virtual ~Block() = default;
     Mixer *mixer = nullptr;
     FeedForward *feed_forward = nullptr;
     Norm *mixer_norm = nullptr, *feed_forward_norm = nullptr;
+    Norm *mixer_post_norm = nullptr, *feed_forward_post_norm = nullptr;   // on a sublayer's output, before the residual add
+    // refuses a layer this arrangement cannot run (called once, when the model is built)
+    virtual void check_layer() const;
+    // true: the block hands the NEXT block's first norm over finished (xw = the normalised rows, tiles == 0) instead of
+    // started, and takes its own that way; between blocks of different habits nothing is handed over
+    virtual bool finished_norms() const { return false; }
     // Runs the block on x in place.  pending: the mixer's norm already started by whoever produced x;
     // next_norm: the norm that will read x after this block, to be started by the block's last projection.
     // Returns the started next_norm (or an undefined DeferredNorm).
@@ -184,6 +192,13 @@ std::unique_ptr<Block> build_block(const std::string &kind, Runtime &rt);
 const char *role_name(int role);
 void register_external_part(int role, const std::string &kind, const fg_part_vtable &vt);
 
+// the built-in kinds that live in other files than parts.cpp (called once, under the registry's lock)
+void add_recurrent_kinds(std::map<std::string, PartFactory> &mixers);
+void add_expert_kinds(std::map<std::string, PartFactory> &feed_forwards);
+
+// a part's tensor by its local name (an internal error if the model did not hand it over)
+const Weight &tensor_of(const std::map<std::string, Weight> &tensors, const char *name);
+
 // parameter access with the messages of a spec error
 long long param_int(const Json &params, const char *key, const char *part);
 long long param_int(const Json &params, const char *key, long long dflt, const char *part);
@@ -218,10 +233,18 @@ private:
     bool fast_ = false;
 };
 
+// What an attention mixer asks of the kernels: sizes, the score scale and which keys a row sees.
+struct AttentionShape {
+    int n_heads = 0, n_kv_heads = 0, head_dim = 0, v_head_dim = 0;
+    float scale = 1.f;
+    int window = 0;                   // 0: every earlier key; w: the last w
+    int keep_first = 0;               // with a window: the sequence's first keys stay visible
+    bool rotate = true;               // false: scores do not depend on positions (no tables are read)
+};
 // Rotary encoding of q (and k), cache append (when the entry owns its cache) and attention of a step's
-// rows; picks kernels by dtype, sizes and step shape.  qkv: [M, H*hd (+ 2*KV*hd)].
+// rows; picks kernels by dtype, sizes and step shape.  qkv: [M, H*hd (+ KV*hd + KV*hdv)].
 Tensor rope_attention(Runtime &rt, const Tensor &qkv, const Batch &batch, const LayerIO &io, const float *cos_t,
-                      const float *sin_t, int n_heads, int n_kv_heads, int head_dim, float scale, int window);
+                      const float *sin_t, const AttentionShape &shape);
 int decode_splits(int n_sm, int n_seq, int n_heads, int n_kv_heads, int table_width, int head_dim);
 
 // llama3 frequency divisors per rotary pair (all ones without scaling)

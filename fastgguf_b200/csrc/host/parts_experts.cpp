@@ -1,0 +1,121 @@
+// Feed-forwards beside SwiGLU: the plain two-matrix one, and the mixture of experts.
+//
+// "mlp":  down(act(up x)); activation "relu2": act(z) = max(z, 0)^2.
+//
+// "moe":  n_experts small gated feed-forwards, of which a row uses top_k.  Router logits z = W_router x are float32
+//         (the contraction takes the activations as they are and accumulates in float32).  router "sigmoid_input":
+//         scores s = sigmoid(z); the top_k largest are chosen; an expert's weight is its own score, not renormalised,
+//         and multiplies the expert's INPUT: out = sum_e expert_e(s_e x).  Expert: g = min(W_gate x, limit),
+//         u = clamp(W_up x, -limit, limit), y = g sigmoid(alpha g) (u + 1), output W_down y.  Because both first
+//         contractions are linear, s_e is applied to their float32 results.
+//         Rows are grouped by expert on the device (experts.cu); the host never learns the routing, so a recorded decode
+//         step replays with whatever the router chooses.
+#include <cmath>
+
+#include "parts.hpp"
+
+namespace fg {
+
+class PlainMLP : public FeedForward {
+public:
+    PlainMLP(const Json &p) : E_((int)param_int(p, "hidden_size", "mlp")), F_((int)param_int(p, "d_ff", "mlp")) {
+        if (E_ <= 0 || F_ <= 0) fail(FG_E_CONFIG, "mlp: sizes must be positive");
+        const Json &a = p.get("activation");
+        std::string act = a.is_string() ? a.as_string() : "relu2";
+        if (act != "relu2") fail(FG_E_CONFIG, "mlp: activation '" + act + "' is not known (known: relu2)");
+    }
+    std::vector<TensorDecl> tensor_decls() const override { return {{"up_proj.weight", {F_, E_}}, {"down_proj.weight", {E_, F_}}}; }
+    void load(const std::map<std::string, Weight> &tensors, Runtime &) override {
+        up_ = Linear(tensor_of(tensors, "up_proj.weight"));
+        down_ = Linear(tensor_of(tensors, "down_proj.weight"));
+    }
+    DeferredNorm forward(Runtime &rt, const Tensor &xn, const DeferredNorm *, const Batch &, Tensor &residual, Norm *emit_norm) override {
+        Tensor t = up_.forward(rt, xn, nullptr, Tensor(), rt.dtype, false, nullptr, nullptr);
+        if (t.rows > 0) FG_LAUNCH("core", fg_activation, t.data, t.dtype, (long long)t.rows * t.ld, 0, rt.stream);
+        DeferredNorm started;
+        down_.forward(rt, t, nullptr, residual, FG_F32, true, emit_norm, &started);
+        return started;
+    }
+
+private:
+    int E_, F_;
+    Linear up_, down_;
+};
+
+class MoEFeedForward : public FeedForward {
+public:
+    MoEFeedForward(const Json &p) {
+        const char *me = "moe";
+        E_ = (int)param_int(p, "hidden_size", me);
+        F_ = (int)param_int(p, "d_ff", me);
+        X_ = (int)param_int(p, "n_experts", me);
+        top_ = (int)param_int(p, "top_k", me);
+        limit_ = (float)param_float(p, "limit", me);
+        alpha_ = (float)param_float(p, "alpha", 1.702, me);
+        if (E_ <= 0 || F_ <= 0 || X_ <= 0 || top_ <= 0) fail(FG_E_CONFIG, "moe: sizes must be positive");
+        if (top_ > X_) fail(FG_E_CONFIG, format("moe: top_k %d exceeds the %d experts", top_, X_));
+        if (X_ > 256 || top_ > 8) fail(FG_E_CONFIG, "moe: the routing kernel takes up to 256 experts and top_k up to 8");
+        if (!(limit_ > 0.f)) fail(FG_E_CONFIG, "moe: limit must be positive");
+        const Json &r = p.get("router");
+        std::string kind = r.is_string() ? r.as_string() : "sigmoid_input";
+        if (kind != "sigmoid_input") fail(FG_E_CONFIG, "moe: router '" + kind + "' is not known (known: sigmoid_input)");
+    }
+    std::vector<TensorDecl> tensor_decls() const override {
+        std::vector<TensorDecl> d = {{"router.weight", {X_, E_}}};
+        for (int e = 0; e < X_; e++) {
+            std::string pre = "experts." + std::to_string(e) + ".";
+            d.push_back({pre + "gate_proj.weight", {F_, E_}});
+            d.push_back({pre + "up_proj.weight", {F_, E_}});
+            d.push_back({pre + "down_proj.weight", {E_, F_}});
+        }
+        return d;
+    }
+    void load(const std::map<std::string, Weight> &tensors, Runtime &rt) override {
+        router_ = Linear(tensor_of(tensors, "router.weight"));
+        // experts one after another: [X, 2F, E] (gate rows, then up rows) and [X, E, F], in the engine's dtype
+        std::vector<Weight> in, out;
+        for (int e = 0; e < X_; e++) {
+            std::string pre = "experts." + std::to_string(e) + ".";
+            in.push_back(tensor_of(tensors, (pre + "gate_proj.weight").c_str()));
+            in.push_back(tensor_of(tensors, (pre + "up_proj.weight").c_str()));
+            out.push_back(tensor_of(tensors, (pre + "down_proj.weight").c_str()));
+        }
+        w_in_ = concat_rows(in, rt.dtype, rt.stream);
+        w_out_ = concat_rows(out, rt.dtype, rt.stream);
+    }
+    DeferredNorm forward(Runtime &rt, const Tensor &xn, const DeferredNorm *, const Batch &, Tensor &residual, Norm *) override {
+        const int M = (int)xn.rows, P = M * top_;
+        if (M == 0) return DeferredNorm();
+        if (xn.dtype != rt.dtype) fail(FG_E_INTERNAL, "moe: the input must be in the engine's dtype");
+        // plain contraction: float32 accumulation of the activations as they are, float32 logits
+        Tensor z = rt.arena->matrix(M, X_, FG_F32);
+        const Tensor &R = router_.weight().t;
+        FG_LAUNCH("core", fg_gemm_generic, xn.data, xn.dtype, (int)xn.ld, R.data, R.dtype, (int)R.ld, z.data, FG_F32, (int)z.ld, 0, M, X_, E_,
+                  rt.stream);
+        int *ints = (int *)rt.arena->alloc(((size_t)3 * P + X_ + 1) * sizeof(int));
+        int *pair_expert = ints, *order = ints + P, *slot_of = ints + 2 * P, *offsets = ints + 3 * P;
+        float *pair_weight = (float *)rt.arena->alloc((size_t)P * sizeof(float));
+        FG_LAUNCH("mix", fg_moe_route, z.ptr<float>(), M, X_, top_, pair_expert, pair_weight, offsets, order, slot_of, rt.stream);
+        Tensor y = rt.arena->matrix(P, F_, rt.dtype);
+        FG_LAUNCH("mix", fg_moe_first, xn.data, (int)xn.ld, w_in_.t.data, y.data, (int)y.ld, rt.dtype, pair_expert, offsets, order, pair_weight,
+                  M, X_, top_, F_, E_, limit_, alpha_, rt.stream);
+        Tensor o = rt.arena->matrix(P, E_, FG_F32);
+        FG_LAUNCH("mix", fg_moe_second, y.data, (int)y.ld, w_out_.t.data, o.ptr<float>(), (int)o.ld, rt.dtype, pair_expert, offsets, order, M,
+                  X_, top_, F_, E_, rt.stream);
+        FG_LAUNCH("mix", fg_moe_combine, o.ptr<float>(), (int)o.ld, slot_of, residual.ptr<float>(), M, top_, E_, 1, rt.stream);
+        return DeferredNorm();
+    }
+
+private:
+    int E_ = 0, F_ = 0, X_ = 0, top_ = 0;
+    float limit_ = 0.f, alpha_ = 1.702f;
+    Linear router_;
+    Weight w_in_, w_out_;
+};
+
+void add_expert_kinds(std::map<std::string, PartFactory> &ffs) {
+    ffs["mlp"] = [](Runtime &, const Json &p, BuildContext &) { return std::make_unique<PlainMLP>(p); };
+    ffs["moe"] = [](Runtime &, const Json &p, BuildContext &) { return std::make_unique<MoEFeedForward>(p); };
+}
+
+}  // namespace fg

@@ -1,0 +1,135 @@
+// Mixers that carry a state of fixed size from token to token instead of keys and values per position.
+//
+// "retention": linear attention with a fixed decay per head and neither softmax nor denominator.  With the layer's
+// normalised input h, per head (q, k of size head_dim, v of size v_head_dim):
+//     q = W_q h, k = W_k h, v = W_v h, g = W_g h       no biases; the four projections are ONE contraction
+//     q, k rotated by the position encoding (if any); k times k_scale afterwards
+//     S_t = decay_head S_(t-1) + k_t v_t^T,  o_t = S_t^T q_t
+//     y = concat_heads(o / sqrt(mean(o^2) + eps)) * silu(g),  output W_o y
+// The state S [heads, head_dim, v_head_dim] is float32 whatever the engine's dtype, one row of the engine's state pool
+// per sequence slot (zeroed when a sequence takes the slot), and so are the projections' results that enter the
+// recurrence: the contraction writes float32 and the kernels of retention.cu keep rotation, decay powers, scores, the
+// unit norm and the gate in float32; y takes the engine's dtype for the output projection.
+// A decode step and short portions walk their tokens one after another with S in shared memory; portions of
+// `chunk_threshold` tokens and more run in chunks over all sequences at once (retention.cu says how).
+#include <cmath>
+
+#include "parts.hpp"
+
+namespace fg {
+
+class RetentionMixer : public Mixer {
+public:
+    RetentionMixer(const Json &p, BuildContext &ctx) {
+        const char *me = "retention";
+        E_ = (int)param_int(p, "hidden_size", me);
+        H_ = (int)param_int(p, "n_heads", me);
+        dk_ = (int)param_int(p, "head_dim", me);
+        dv_ = (int)param_int(p, "v_head_dim", dk_, me);
+        eps_ = (float)param_float(p, "eps", me);
+        k_scale_ = (float)param_float(p, "k_scale", 1.0 / std::sqrt((double)dk_), me);
+        if (E_ <= 0 || H_ <= 0 || dk_ <= 0 || dv_ <= 0) fail(FG_E_CONFIG, "retention: sizes must be positive");
+        if (dk_ % 2) fail(FG_E_CONFIG, format("retention: head_dim must be even, got %d", dk_));
+        if (dv_ > 256) fail(FG_E_CONFIG, format("retention: v_head_dim %d exceeds 256, the largest the kernels take", dv_));
+        if ((size_t)dk_ * dv_ > 40 * 1024) fail(FG_E_CONFIG, "retention: a head's state exceeds what the kernels hold in shared memory");
+        if (!(eps_ > 0.f)) fail(FG_E_CONFIG, "retention: eps must be positive");
+        const Json &d = p.get("decay");
+        if (!d.is_array() || (int)d.size() != H_) fail(FG_E_CONFIG, format("retention: 'decay' must list one number for each of the %d heads", H_));
+        for (auto &v : d.items()) {
+            if (!v.is_number() || v.is_bool() || !(v.as_double() >= 0.0) || !(v.as_double() <= 1.0))
+                fail(FG_E_CONFIG, "retention: a decay must be a number in [0, 1], got " + v.dump());
+            decay_.push_back((float)v.as_double());
+            all_positive_ = all_positive_ && v.as_double() > 0.0;
+        }
+        const Json &pos = p.get("position");
+        if (!pos.is_null()) {
+            position_ = dynamic_cast<PositionEncoding *>(ctx.nested(FG_ROLE_POSITION, pos));
+            if (!position_) fail(FG_E_CONFIG, "retention: 'position' is not a position encoding");
+            if (position_->head_dim() != dk_)
+                fail(FG_E_CONFIG, format("retention: the position encoding is built for head_dim %d, the mixer has %d", position_->head_dim(), dk_));
+        }
+    }
+    std::vector<TensorDecl> tensor_decls() const override {
+        int64_t Q = (int64_t)H_ * dk_, V = (int64_t)H_ * dv_;
+        return {{"q_proj.weight", {Q, E_}}, {"k_proj.weight", {Q, E_}}, {"v_proj.weight", {V, E_}}, {"g_proj.weight", {V, E_}},
+                {"o_proj.weight", {E_, V}}};
+    }
+    int64_t state_bytes() const override { return (int64_t)H_ * dk_ * dv_ * (int64_t)sizeof(float); }
+    void load(const std::map<std::string, Weight> &tensors, Runtime &rt) override {
+        Weight q = tensor_of(tensors, "q_proj.weight"), k = tensor_of(tensors, "k_proj.weight");
+        const Weight &v = tensor_of(tensors, "v_proj.weight"), &g = tensor_of(tensors, "g_proj.weight");
+        if (position_ && !position_->permutation().empty()) {
+            // the kernels rotate pairs (j, j + head_dim / 2); q . k does not change under a common permutation of both
+            const std::vector<int> &perm = position_->permutation();
+            std::vector<int64_t> rows;
+            for (int h = 0; h < H_; h++)
+                for (int i = 0; i < dk_; i++) rows.push_back((int64_t)h * dk_ + perm[(size_t)i]);
+            q = gather_rows(q, rows, rt.stream);
+            k = gather_rows(k, rows, rt.stream);
+        }
+        bool same = q.t.dtype == k.t.dtype && k.t.dtype == v.t.dtype && v.t.dtype == g.t.dtype;
+        proj_ = Linear(concat_rows({q, k, v, g}, same ? q.t.dtype : FG_F32, rt.stream));
+        o_ = Linear(tensor_of(tensors, "o_proj.weight"));
+        decay_dev_ = make_weight(1, H_, FG_F32, "retention decays");
+        FG_CUDA(cudaMemcpyAsync(decay_dev_.t.data, decay_.data(), decay_.size() * sizeof(float), cudaMemcpyHostToDevice, rt.stream));
+        FG_CUDA(cudaStreamSynchronize(rt.stream));
+    }
+    void prepare(Runtime &rt, int max_positions) override {
+        if (position_) { position_->prepare(rt, max_positions); return; }
+        // no rotation: identity tables, so that one kernel serves both
+        if (ident_cos_.buffer && ident_positions_ >= max_positions) return;
+        int half = dk_ / 2;
+        std::vector<float> c((size_t)max_positions * half, 1.0f);
+        ident_cos_ = make_weight(max_positions, half, FG_F32, "identity rotation tables");
+        ident_sin_ = make_weight(max_positions, half, FG_F32, "identity rotation tables");
+        FG_CUDA(cudaMemcpyAsync(ident_cos_.t.data, c.data(), c.size() * 4, cudaMemcpyHostToDevice, rt.stream));
+        FG_CUDA(cudaMemsetAsync(ident_sin_.t.data, 0, c.size() * 4, rt.stream));
+        FG_CUDA(cudaStreamSynchronize(rt.stream));
+        ident_positions_ = max_positions;
+    }
+    DeferredNorm forward(Runtime &rt, const Tensor &xn, const DeferredNorm *, const Batch &b, const LayerIO &io, Tensor &residual,
+                         Norm *emit_norm) override {
+        if (!io.state || io.state_bytes < state_bytes()) fail(FG_E_INTERNAL, "retention: the schedule entry has no state rows");
+        const float *cos_t = position_ ? position_->cos_table() : ident_cos_.t.ptr<float>();
+        const float *sin_t = position_ ? position_->sin_table() : ident_sin_.t.ptr<float>();
+        // what enters the recurrence stays float32: the contraction accumulates in float32 and writes it as it is
+        Tensor proj = proj_.forward(rt, xn, nullptr, Tensor(), FG_F32, false, nullptr, nullptr);
+        const int M = (int)proj.rows;
+        Tensor y = rt.arena->matrix(M, (int64_t)H_ * dv_, rt.dtype);
+        const int *host_cu = b.host_cu_rows.empty() ? nullptr : b.host_cu_rows.data();
+        const int RC = FG_KERNEL("mix", fg_retention_chunk_tokens)();
+        bool chunked = host_cu && !b.single_token && all_positive_ && b.max_new >= chunk_threshold_ &&
+                       FG_KERNEL("mix", fg_retention_chunked_ok)(dk_, dv_);
+        if (chunked) {
+            // the host knows only how many chunks the step has; the kernels plan them from the step's row offsets
+            int n_chunks = 0;
+            for (int s = 0; s < b.n_seq; s++) n_chunks += (host_cu[s + 1] - host_cu[s] + RC - 1) / RC;
+            int *plan = (int *)rt.arena->alloc(((size_t)2 * n_chunks + b.n_seq + 1) * sizeof(int));
+            float *U = (float *)rt.arena->alloc((size_t)n_chunks * H_ * dk_ * dv_ * sizeof(float));
+            FG_LAUNCH("mix", fg_retention_chunked, proj.ptr<float>(), (int)proj.ld, y.data, y.dtype, (int)y.ld, b.positions, b.cu_rows,
+                      b.slots, cos_t, sin_t, decay_dev_.t.ptr<float>(), (float *)io.state, plan, U, b.n_seq, n_chunks, H_, dk_, dv_,
+                      k_scale_, eps_, rt.stream);
+        } else {
+            FG_LAUNCH("mix", fg_retention, proj.ptr<float>(), (int)proj.ld, y.data, y.dtype, (int)y.ld, b.positions, b.cu_rows, b.slots, cos_t,
+                      sin_t, decay_dev_.t.ptr<float>(), (float *)io.state, b.n_seq, H_, dk_, dv_, k_scale_, eps_, rt.stream);
+        }
+        DeferredNorm started;
+        o_.forward(rt, y, nullptr, residual, FG_F32, true, emit_norm, &started);
+        return started;
+    }
+
+private:
+    int E_ = 0, H_ = 0, dk_ = 0, dv_ = 0, chunk_threshold_ = 16, ident_positions_ = 0;
+    float eps_ = 0.f, k_scale_ = 1.f;
+    bool all_positive_ = true;
+    std::vector<float> decay_;
+    PositionEncoding *position_ = nullptr;
+    Linear proj_, o_;
+    Weight decay_dev_, ident_cos_, ident_sin_;
+};
+
+void add_recurrent_kinds(std::map<std::string, PartFactory> &mixers) {
+    mixers["retention"] = [](Runtime &, const Json &p, BuildContext &c) { return std::make_unique<RetentionMixer>(p, c); };
+}
+
+}  // namespace fg

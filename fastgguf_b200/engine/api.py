@@ -132,8 +132,9 @@ class Engine:
         opts.max_batch, opts.max_tokens, opts.max_seq_len = int(max_batch), int(max_tokens), int(max_seq_len or 0)
         opts.device = int(dev.split(":")[1]) if ":" in dev else 0
         opts.use_graphs, opts.verbose = int(bool(use_graphs)), int(bool(verbose))
-        # the libraries the host opens by name are compiled here, on first use, for what this dtype needs
-        capi.ensure_kernel_libraries(opts.dtype)
+        # the libraries the host opens by name are compiled here, on first use, for what this model and dtype need
+        self.spec = spec if spec is not None else (spec_from_config(config) if config is not None else None)
+        capi.ensure_kernel_libraries(opts.dtype, self.spec.to_json() if hasattr(self.spec, "to_json") else self.spec)
         out = c_void_p()
         l = capi.lib()
         if spec is not None:
@@ -154,7 +155,6 @@ class Engine:
         self._handle = out
         self._info = None
         self.cache = CacheView(self)
-        self.spec = spec if spec is not None else spec_from_config(config)
 
     def __del__(self):
         h, self._handle = getattr(self, "_handle", None), None

@@ -41,15 +41,25 @@ class PartSpec:
 
 @dataclass
 class LayerSpec:
-    block: str                     # arrangement kind, e.g. "prenorm"
+    block: str                     # arrangement kind, e.g. "prenorm", "sandwich"
     mixer: PartSpec
-    feed_forward: PartSpec
+    feed_forward: Optional[PartSpec]           # None: a layer of a mixer alone
     mixer_norm: PartSpec
-    feed_forward_norm: PartSpec
+    feed_forward_norm: Optional[PartSpec]
+    #: norms on a sublayer's output, before it joins the residual stream (block "sandwich")
+    mixer_post_norm: Optional[PartSpec] = None
+    feed_forward_post_norm: Optional[PartSpec] = None
 
     def to_json(self) -> dict:
-        return {"block": self.block, "mixer": self.mixer.to_json(), "feed_forward": self.feed_forward.to_json(),
-                "mixer_norm": self.mixer_norm.to_json(), "feed_forward_norm": self.feed_forward_norm.to_json()}
+        def opt(p):
+            return p.to_json() if p is not None else None
+        j = {"block": self.block, "mixer": self.mixer.to_json(), "feed_forward": opt(self.feed_forward),
+             "mixer_norm": self.mixer_norm.to_json(), "feed_forward_norm": opt(self.feed_forward_norm)}
+        if self.mixer_post_norm is not None:
+            j["mixer_post_norm"] = self.mixer_post_norm.to_json()
+        if self.feed_forward_post_norm is not None:
+            j["feed_forward_post_norm"] = self.feed_forward_post_norm.to_json()
+        return j
 
 
 @dataclass
@@ -87,11 +97,14 @@ class ModelSpec:
     @classmethod
     def from_json(cls, j: dict) -> "ModelSpec":
         P = PartSpec.from_json
+
+        def O(v):
+            return P(v) if v else None
         return cls(
             hidden_size=j["hidden_size"], vocab_size=j["vocab_size"], max_positions=j["max_positions"],
             embedding=P(j["embedding"]), final_norm=P(j["final_norm"]), head=P(j["head"]),
-            layers=[LayerSpec(l["block"], P(l["mixer"]), P(l["feed_forward"]), P(l["mixer_norm"]), P(l["feed_forward_norm"]))
-                    for l in j["layers"]],
+            layers=[LayerSpec(l["block"], P(l["mixer"]), O(l.get("feed_forward")), P(l["mixer_norm"]), O(l.get("feed_forward_norm")),
+                              O(l.get("mixer_post_norm")), O(l.get("feed_forward_post_norm"))) for l in j["layers"]],
             schedule=[RunSpec(r["layer"], r.get("cache_from")) for r in j["schedule"]],
             stop_token_ids=tuple(j.get("stop_token_ids") or ()), ignored_tensors=tuple(j.get("ignored_tensors") or ()),
         )

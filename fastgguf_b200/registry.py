@@ -1,6 +1,6 @@
 """One registry from an architecture's name to its model - the host's (``csrc/host/config.cpp``).
 
-``architectures[0]`` of config.json selects the reader of the typed configuration and the function that
+``architectures[0]`` (or ``architecture``) of config.json selects the reader of the typed configuration and the function that
 turns it into a model spec (which parts, in which layers, run in which order, with which checkpoint
 tensor names).  Everything else (loader, cache, step function, generation, replay) works from the spec and
 never asks which model it is in.  The reference picks its code path by ``strcmp`` on
@@ -16,9 +16,10 @@ from typing import Callable
 from . import capi
 from .config.base import ModelConfig
 from .config.llama import LlamaConfig
+from .config.zirivik import ZirivikConfig
 from .engine.spec import ModelSpec
 
-_CLASSES = {"LlamaForCausalLM": LlamaConfig}
+_CLASSES = {"LlamaForCausalLM": LlamaConfig, "Zirivik": ZirivikConfig}
 _keep_alive = []
 
 
@@ -50,6 +51,8 @@ def register_architecture(name: str, build_spec: Callable[[dict], dict]) -> None
 
 def config_from_dict(d: dict) -> ModelConfig:
     archs = d.get("architectures") if isinstance(d, dict) else None
+    if archs is None and isinstance(d, dict) and isinstance(d.get("architecture"), str):
+        archs = [d["architecture"]]
     cls = _CLASSES.get(archs[0], ModelConfig) if isinstance(archs, list) and archs else ModelConfig
     return ModelConfig.from_dict.__func__(cls, d)
 
