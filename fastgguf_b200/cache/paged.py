@@ -1,8 +1,9 @@
 """The cache's bookkeeping, as Python sees it: a view of the host's ``PagedKVCache`` (``csrc/host/cache.cpp``).
 
 A slot per live sequence holds its length and, per cache group, the pages it owns; a cache group is the set of
-schedule entries whose mixers asked for the same (KV heads, head size, window) and has storage of its own; a
-windowed group gives pages back as they leave the window; page 0 is never handed out.  An engine holds such a
+schedule entries whose mixers asked for the same (KV heads, head sizes, window, kept first positions) and has storage
+of its own; a windowed group gives pages back as they leave the window, except those of the kept first positions;
+page 0 is never handed out.  An engine holds such a
 cache with device pools; this class creates the bookkeeping alone (no device memory), which is what the host-side
 tests drive.  Reference: per-layer arrays ``[capacity][kv_dim]`` for one sequence (fastgguf.c:4114-4115,
 :4449-4450), rings for sliding-window layers (:4427-4436), borrowed caches (:4745-4751).
@@ -25,15 +26,19 @@ __all__ = ["CacheError", "CacheFull", "CacheRequest", "PagedKVCache", "cache_byt
 @dataclass(frozen=True)
 class CacheRequest:
     """Keys and values a mixer keeps per position.  ``window`` None keeps every position; an integer keeps the
-    last ``window`` positions.  Requests that agree in all fields share a cache group."""
+    last ``window`` positions and, with ``keep_first``, the sequence's first positions as well.  ``v_head_dim``: values
+    of another head size than the keys.  Requests that agree in all fields share a cache group."""
 
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    v_head_dim: Optional[int] = None
+    keep_first: int = 0
 
 
 def _requests_json(requests: Dict[int, CacheRequest]) -> bytes:
-    return json.dumps([{"entry": int(e), "n_kv_heads": r.n_kv_heads, "head_dim": r.head_dim, "window": r.window}
+    return json.dumps([{"entry": int(e), "n_kv_heads": r.n_kv_heads, "head_dim": r.head_dim, "window": r.window,
+                        "v_head_dim": r.v_head_dim, "keep_first": int(r.keep_first)}
                        for e, r in sorted(requests.items())]).encode("utf-8")
 
 

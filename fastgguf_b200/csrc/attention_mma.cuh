@@ -101,7 +101,8 @@ __device__ __forceinline__ float ex2(float x) {
 // On return s holds the probabilities 2^(score - m_new) and o, l are rescaled.
 template <int NO, bool MASK>
 __device__ __forceinline__ void softmax_update(float (&s)[8][4], float (&o)[NO][4], float (&m)[2], float (&l)[2],
-                                               float scale_log2, int key0, const int (&lo)[2], const int (&hi)[2], int lane) {
+                                               float scale_log2, int key0, const int (&lo)[2], const int (&hi)[2], int lane,
+                                               int keep = 0 /* keys below it stay visible in front of lo */) {
     const int c0 = key0 + 2 * (lane & 3);
     float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
@@ -110,7 +111,7 @@ __device__ __forceinline__ void softmax_update(float (&s)[8][4], float (&o)[NO][
         for (int e = 0; e < 4; e++) {
             int i = e >> 1, key = c0 + 8 * j + (e & 1);
             float v = s[j][e] * scale_log2;
-            if (MASK) v = (key >= lo[i] && key <= hi[i]) ? v : -INFINITY;
+            if (MASK) v = ((key >= lo[i] || key < keep) && key <= hi[i]) ? v : -INFINITY;
             s[j][e] = v;
             mx[i] = fmaxf(mx[i], v);
         }

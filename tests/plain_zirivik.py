@@ -73,8 +73,10 @@ def retention_mixer(h, positions, W, p, mc, eps, state):
     q = (h @ W[p + "q"].T).reshape(T, H, dk)
     k = (h @ W[p + "k"].T).reshape(T, H, dk)
     v = (h @ W[p + "v"].T).reshape(T, H, dv)
-    q = rotate_front(q, positions, mc["rot"]["dims"], mc["rot"]["base"])
-    k = rotate_front(k, positions, mc["rot"]["dims"], mc["rot"]["base"]) * dk ** -0.5
+    if mc.get("rot"):                                   # a mixer without "rot" does not rotate
+        q = rotate_front(q, positions, mc["rot"]["dims"], mc["rot"]["base"])
+        k = rotate_front(k, positions, mc["rot"]["dims"], mc["rot"]["base"])
+    k = k * dk ** -0.5
     decay = torch.tensor(mc["decay"], dtype=h.dtype)[:, None, None]
     o = torch.empty(T, H, dv, dtype=h.dtype)
     for t in range(T):
@@ -94,7 +96,7 @@ def attention_mixer(h, positions, W, p, mc, keys, values):
     H, G, dk, dv = mc["heads"], mc["kv_heads"], mc["dim"], mc["vdim"]
     T, P = h.shape[0], keys.shape[0]
     q = (h @ W[p + "q"].T).reshape(T, H, dk)
-    size, keep = mc["mask"]["size"], mc["mask"]["keep_first"]
+    size, keep = (mc["mask"]["size"], mc["mask"]["keep_first"]) if mc.get("mask") else (P + 1, 0)   # no mask: every earlier key
     mask = torch.tensor([[visible(int(i), j, size, keep) for j in range(P)] for i in positions])
     out = torch.empty(T, H, dv, dtype=h.dtype)
     for head in range(H):

@@ -152,3 +152,33 @@ def test_random_traffic_keeps_the_invariants():
         c.release(s)
     c.check()
     assert c.free_pages() == 12
+
+
+def test_kept_first_positions_keep_their_pages():
+    """A windowed group whose mixers go on reading a sequence's first positions never gives those pages back."""
+    req = {0: CacheRequest(1, 16, window=70), 1: CacheRequest(1, 16, window=70, keep_first=5),
+           2: CacheRequest(1, 16, window=70, keep_first=65)}
+    c = PagedKVCache(req, max_tokens=2048, max_seq_len=2048, n_slots=2)
+    assert len(c.groups) == 3 and [g["keep_first"] for g in c.groups] == [0, 5, 65]
+    s = c.acquire()
+    c.reserve([(s, 300)]); c.commit([(s, 300)])
+    # positions 230.. are in the window: pages 3 and 4; kept: none, page 0, pages 0 and 1
+    assert [c.free_pages(g) for g in range(3)] == [32 - 2, 32 - 3, 32 - 4]
+    first = [c.block_table(g, [s], 5)[0].tolist() for g in range(3)]
+    assert first[0][:3] == [0, 0, 0] and first[1][0] > 0 and first[1][1:3] == [0, 0] and first[2][0] > 0 and first[2][1] > 0
+    for _ in range(200):
+        c.reserve([(s, 1)]); c.commit([(s, 1)])
+        c.check()
+    after = [c.block_table(g, [s], 8)[0].tolist() for g in range(3)]
+    assert after[1][0] == first[1][0] and after[2][:2] == first[2][:2]          # the same pages all along
+    assert after[1][1:5] == [0, 0, 0, 0] and after[2][2:5] == [0, 0, 0]
+    c.release(s)
+    assert [c.free_pages(g) for g in range(3)] == [32, 32, 32]
+
+
+def test_values_of_another_head_size():
+    b = cache_bytes({0: CacheRequest(2, 16, v_head_dim=40)}, 256, dtype="float32")
+    assert b["bytes_per_token"] == 4 * 2 * (16 + 40)
+    same = PagedKVCache({0: CacheRequest(2, 16), 1: CacheRequest(2, 16, v_head_dim=16), 2: CacheRequest(2, 16, v_head_dim=8)},
+                        max_tokens=256, max_seq_len=256, n_slots=1)
+    assert same.group_of_entry == {0: 0, 1: 0, 2: 1}
