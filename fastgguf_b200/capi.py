@@ -258,8 +258,8 @@ def kernel_modules_for(spec_json, dtype_code: int) -> tuple:
             part = layer.get(role) or {}
             kinds.add(part.get("kind"))
             p = part.get("params") or {}
-            if role == "mixer" and part.get("kind") == "gqa_attention" and p.get("head_dim") in (64, 128) and p.get("v_head_dim", p.get("head_dim")) == p.get("head_dim") \
-                    and not (p.get("window") and p.get("keep_first")):
+            if role == "mixer" and part.get("kind") == "gqa_attention" and p.get("head_dim") in (64, 128) \
+                    and p.get("v_head_dim", p.get("head_dim")) == p.get("head_dim"):
                 fast_attention = True
     builtin = {"gqa_attention", "swiglu", "retention", "mlp", "moe", None}
     if dtype_code == FG_BF16 and (fast_attention or kinds - builtin):

@@ -42,6 +42,7 @@ struct RopeArgs {
     const float *cos_t, *sin_t;      // [positions, HD / 2]
     bf16 *k_pool, *v_pool;           // the cache, writable
     int q_heads;                     // H: k starts at q + H * HD, v at q + (H + KV) * HD
+    int keep_first;                  // with a window: the sequence's first keys stay visible (both forms of the kernel)
 };
 
 template <int HD, bool CLUSTER, bool FUSE>
@@ -68,10 +69,16 @@ attn_decode_kernel(const bf16 *__restrict__ q, int ldq, const int *__restrict__ 
     // pool is appended to by this kernel alone.  A caller that reorders that must launch without the overlap.
     const int pos = positions[b];
     const int lo_key = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-    const int first_page = lo_key / PAGE, n_pages = pos / PAGE - first_page + 1;
+    // Pages are walked by a running index: first the pages of the kept first keys that lie wholly in front of the
+    // window's first page, then the window's pages; page_of gives the page of the sequence behind an index.
+    const int keep = window > 0 ? rope.keep_first : 0;
+    const int first_page = lo_key / PAGE;
+    const int n_kept = min((keep + PAGE - 1) / PAGE, first_page);
+    const int n_pages = n_kept + pos / PAGE - first_page + 1;
     const int per = (n_pages + n_splits - 1) / n_splits;
-    const int p_begin = first_page + split * per, p_end = min(first_page + n_pages, p_begin + per);
+    const int p_begin = split * per, p_end = min(n_pages, p_begin + per);
     const int *bt = block_table + (size_t)b * table_width;
+    auto page_of = [&](int i) { return i < n_kept ? i : first_page + (i - n_kept); };
 
     uint8_t *kbuf = smem + (size_t)warp * 2 * TILE_BYTES, *vbuf = kbuf + TILE_BYTES;
     const uint32_t ks = smem_addr(kbuf), vs = smem_addr(vbuf);
@@ -84,7 +91,7 @@ attn_decode_kernel(const bf16 *__restrict__ q, int ldq, const int *__restrict__ 
 
     int p = p_begin + warp;
     if (p < p_end) {
-        size_t base = ((size_t)bt[p] * KV + kvh) * PAGE * HD;
+        size_t base = ((size_t)bt[page_of(p)] * KV + kvh) * PAGE * HD;
         load_page_warp<HD>(ks, k_pool + base, lane);
         cp_async_commit();
         load_page_warp<HD>(vs, v_pool + base, lane);
@@ -92,7 +99,7 @@ attn_decode_kernel(const bf16 *__restrict__ q, int ldq, const int *__restrict__ 
     }
     if (FUSE) pdl_wait();                      // q, k, v of the new token come from the kernel before
     // the warp that will read the sequence's last page fetches the new token's k and v now, with q
-    const int p_new = pos / PAGE;
+    const int p_new = n_pages - 1;             // the sequence's last page is the walk's last
     const bool mine = FUSE && p_new >= p_begin && p_new < p_end && ((p_new - p_begin) & (DEC_WARPS - 1)) == warp;
     uint4 knew_lo = make_uint4(0, 0, 0, 0), knew_hi = knew_lo, vnew = knew_lo;
     if (mine) {
@@ -133,10 +140,11 @@ attn_decode_kernel(const bf16 *__restrict__ q, int ldq, const int *__restrict__ 
     }
     for (; p < p_end; p += DEC_WARPS) {
         const int pn = p + DEC_WARPS;
-        const size_t nbase = pn < p_end ? ((size_t)bt[pn] * KV + kvh) * PAGE * HD : 0;
+        const size_t nbase = pn < p_end ? ((size_t)bt[page_of(pn)] * KV + kvh) * PAGE * HD : 0;
+        const int rp = page_of(p);             // the page of the sequence this step works on
         cp_async_wait<1>();                    // K of this page has landed (V may still be in flight)
         __syncwarp();
-        const bool newest = FUSE && p == pos / PAGE;      // this page holds the new token's row
+        const bool newest = FUSE && rp == pos / PAGE;     // this page holds the new token's row
         if (newest) {
             // rotated k of the new token -> row pos % 64 of the K tile (and the cache, once per KV head)
             const int off = pos % PAGE;
@@ -159,7 +167,7 @@ attn_decode_kernel(const bf16 *__restrict__ q, int ldq, const int *__restrict__ 
                 *(uint4 *)(kbuf + off * (HD * 2) + ((clo ^ (off & 7)) << 4)) = olo;
                 *(uint4 *)(kbuf + off * (HD * 2) + ((chi ^ (off & 7)) << 4)) = ohi;
                 if (to_cache) {
-                    bf16 *dst = rope.k_pool + (((size_t)bt[p] * KV + kvh) * PAGE + off) * HD;
+                    bf16 *dst = rope.k_pool + (((size_t)bt[rp] * KV + kvh) * PAGE + off) * HD;
                     *(uint4 *)(dst + j0) = olo;
                     *(uint4 *)(dst + HD / 2 + j0) = ohi;
                 }
@@ -173,10 +181,10 @@ attn_decode_kernel(const bf16 *__restrict__ q, int ldq, const int *__restrict__ 
         __syncwarp();
         if (pn < p_end) load_page_warp<HD>(ks, k_pool + nbase, lane);
         cp_async_commit();                     // (possibly empty) group: keeps the wait counts uniform
-        if (p * PAGE + PAGE - 1 <= pos && p * PAGE >= lo_key)
-            softmax_update<HD / 8, false>(s, o, m, l, scale * LOG2E, p * PAGE, lo, hi, lane);
+        if (rp * PAGE + PAGE - 1 <= pos && rp * PAGE >= lo_key)
+            softmax_update<HD / 8, false>(s, o, m, l, scale * LOG2E, rp * PAGE, lo, hi, lane);
         else
-            softmax_update<HD / 8, true>(s, o, m, l, scale * LOG2E, p * PAGE, lo, hi, lane);
+            softmax_update<HD / 8, true>(s, o, m, l, scale * LOG2E, rp * PAGE, lo, hi, lane, keep);
         cp_async_wait<1>();                    // V of this page has landed
         __syncwarp();
         if (newest) {
@@ -185,7 +193,7 @@ attn_decode_kernel(const bf16 *__restrict__ q, int ldq, const int *__restrict__ 
                 uint4 v4 = vnew;
                 *(uint4 *)(vbuf + off * (HD * 2) + ((lane ^ (off & 7)) << 4)) = v4;
                 if (blockIdx.y % chunks == 0)
-                    *(uint4 *)(rope.v_pool + (((size_t)bt[p] * KV + kvh) * PAGE + off) * HD + lane * 8) = v4;
+                    *(uint4 *)(rope.v_pool + (((size_t)bt[rp] * KV + kvh) * PAGE + off) * HD + lane * 8) = v4;
             }
             __syncwarp();
         }
@@ -362,16 +370,18 @@ static int launch_decode_kernel(dim3 grid, int cluster_x, cudaStream_t stream, c
 template <int HD>
 static int launch_decode(const void *q, int ldq, void *out, int ldo, const int *positions, const int *block_table,
                          int table_width, const void *k_pool, const void *v_pool, int B, int H, int KV, float scale,
-                         int window, int n_splits, float *part_o, float *part_ml, cudaStream_t stream) {
+                         int window, int keep_first, int n_splits, float *part_o, float *part_ml, cudaStream_t stream) {
     int G = H / KV;
     dim3 grid(n_splits, KV * ((G + 15) / 16), B);
+    RopeArgs extra{};
+    extra.keep_first = keep_first;
     // 2, 4 or 8 splits without scratch memory: merged inside a cluster
     bool cluster = !part_o && (n_splits == 2 || n_splits == 4 || n_splits == 8);
     if (n_splits == 1 || cluster)
         return launch_decode_kernel<HD, true>(grid, cluster ? n_splits : 1, stream, q, ldq, out, ldo, positions, block_table,
-                                              table_width, k_pool, v_pool, KV, G, scale, window, n_splits, nullptr, nullptr);
+                                              table_width, k_pool, v_pool, KV, G, scale, window, n_splits, nullptr, nullptr, extra);
     int e = launch_decode_kernel<HD, false>(grid, 1, stream, q, ldq, out, ldo, positions, block_table, table_width, k_pool,
-                                            v_pool, KV, G, scale, window, n_splits, part_o, part_ml);
+                                            v_pool, KV, G, scale, window, n_splits, part_o, part_ml, extra);
     if (e) return e;
     return fg_launch(attn_decode_merge_kernel<HD>, dim3(H, B), dim3(HD), 0, stream, (const float *)part_o,
                      (const float *)part_ml, n_splits, H, (bf16 *)out, ldo);
@@ -382,35 +392,45 @@ static int launch_decode(const void *q, int ldq, void *out, int ldo, const int *
 // part_o: [B, H, n_splits, HD] f32 and part_ml: [B, H, n_splits, 2] f32 scratch for the two-kernel
 // path; pass null pointers with n_splits 1, 2, 4 or 8 for the path that needs no scratch.
 // Takes HD 64 and 128 and pages of 64; anything else returns FG_ERR_BAD_SIZE.
+// keep_first (with a window): the first keep_first keys of the sequence stay visible.
+extern "C" int fg_attention_decode_kept(const void *q, int ldq, void *out, int ldo, const int *positions,
+                                        const int *block_table, int table_width, const void *k_pool, const void *v_pool,
+                                        int B, int H, int KV, int hd, int page_size, float scale, int window, int keep_first,
+                                        int n_splits, float *part_o, float *part_ml, cudaStream_t stream) {
+    if (B <= 0) return 0;
+    if (KV <= 0 || H <= 0 || keep_first < 0) return FG_ERR_BAD_SIZE;
+    if (page_size != PAGE || H % KV || n_splits < 1 || B > 65535 || ldq % 2 || ((uintptr_t)q & 3)) return FG_ERR_BAD_SIZE;
+    if ((part_o == nullptr) != (part_ml == nullptr)) return FG_ERR_BAD_SIZE;
+    if (!part_o && n_splits != 1 && n_splits != 2 && n_splits != 4 && n_splits != 8) return FG_ERR_BAD_SIZE;
+    if (hd == 64) return launch_decode<64>(q, ldq, out, ldo, positions, block_table, table_width, k_pool, v_pool, B, H, KV, scale, window, keep_first, n_splits, part_o, part_ml, stream);
+    if (hd == 128) return launch_decode<128>(q, ldq, out, ldo, positions, block_table, table_width, k_pool, v_pool, B, H, KV, scale, window, keep_first, n_splits, part_o, part_ml, stream);
+    return FG_ERR_BAD_SIZE;
+}
+
 extern "C" int fg_attention_decode(const void *q, int ldq, void *out, int ldo, const int *positions,
                                    const int *block_table, int table_width, const void *k_pool, const void *v_pool,
                                    int B, int H, int KV, int hd, int page_size, float scale, int window,
                                    int n_splits, float *part_o, float *part_ml, cudaStream_t stream) {
-    if (B <= 0) return 0;
-    if (KV <= 0 || H <= 0) return FG_ERR_BAD_SIZE;
-    if (page_size != PAGE || H % KV || n_splits < 1 || B > 65535 || ldq % 2 || ((uintptr_t)q & 3)) return FG_ERR_BAD_SIZE;
-    if ((part_o == nullptr) != (part_ml == nullptr)) return FG_ERR_BAD_SIZE;
-    if (!part_o && n_splits != 1 && n_splits != 2 && n_splits != 4 && n_splits != 8) return FG_ERR_BAD_SIZE;
-    if (hd == 64) return launch_decode<64>(q, ldq, out, ldo, positions, block_table, table_width, k_pool, v_pool, B, H, KV, scale, window, n_splits, part_o, part_ml, stream);
-    if (hd == 128) return launch_decode<128>(q, ldq, out, ldo, positions, block_table, table_width, k_pool, v_pool, B, H, KV, scale, window, n_splits, part_o, part_ml, stream);
-    return FG_ERR_BAD_SIZE;
+    return fg_attention_decode_kept(q, ldq, out, ldo, positions, block_table, table_width, k_pool, v_pool, B, H, KV, hd, page_size,
+                                    scale, window, 0, n_splits, part_o, part_ml, stream);
 }
 
 // The fused decode step of an attention layer: RoPE of q and of the new k, cache append of k and v, and
 // attention, in one kernel.  qkv: [B, ldq] rows of (q heads | k heads | v heads) straight from the
 // projection; cos/sin: [positions, hd / 2] f32; n_splits 1, 2, 4 or 8 (merged inside a cluster).
-extern "C" int fg_attention_decode_fused(const void *qkv, int ldq, void *out, int ldo, const int *positions,
-                                         const int *block_table, int table_width, void *k_pool, void *v_pool,
-                                         const float *cos_t, const float *sin_t, int B, int H, int KV, int hd,
-                                         int page_size, float scale, int window, int n_splits, cudaStream_t stream) {
+extern "C" int fg_attention_decode_fused_kept(const void *qkv, int ldq, void *out, int ldo, const int *positions,
+                                              const int *block_table, int table_width, void *k_pool, void *v_pool,
+                                              const float *cos_t, const float *sin_t, int B, int H, int KV, int hd,
+                                              int page_size, float scale, int window, int keep_first, int n_splits,
+                                              cudaStream_t stream) {
     if (B <= 0) return 0;
-    if (KV <= 0 || H <= 0) return FG_ERR_BAD_SIZE;
+    if (KV <= 0 || H <= 0 || keep_first < 0) return FG_ERR_BAD_SIZE;
     if (page_size != PAGE || H % KV || B > 65535 || ldq % 8 || ((uintptr_t)qkv & 15) || ((uintptr_t)k_pool & 15) ||
         ((uintptr_t)v_pool & 15) || (n_splits != 1 && n_splits != 2 && n_splits != 4 && n_splits != 8))
         return FG_ERR_BAD_SIZE;
     int G = H / KV;
     dim3 grid(n_splits, KV * ((G + 15) / 16), B);
-    RopeArgs rope{cos_t, sin_t, (bf16 *)k_pool, (bf16 *)v_pool, H};
+    RopeArgs rope{cos_t, sin_t, (bf16 *)k_pool, (bf16 *)v_pool, H, keep_first};
     if (hd == 64)
         return launch_decode_kernel<64, true, true>(grid, n_splits, stream, qkv, ldq, out, ldo, positions, block_table,
                                                     table_width, k_pool, v_pool, KV, G, scale, window, n_splits, nullptr,
@@ -420,6 +440,14 @@ extern "C" int fg_attention_decode_fused(const void *qkv, int ldq, void *out, in
                                                      table_width, k_pool, v_pool, KV, G, scale, window, n_splits, nullptr,
                                                      nullptr, rope);
     return FG_ERR_BAD_SIZE;
+}
+
+extern "C" int fg_attention_decode_fused(const void *qkv, int ldq, void *out, int ldo, const int *positions,
+                                         const int *block_table, int table_width, void *k_pool, void *v_pool,
+                                         const float *cos_t, const float *sin_t, int B, int H, int KV, int hd,
+                                         int page_size, float scale, int window, int n_splits, cudaStream_t stream) {
+    return fg_attention_decode_fused_kept(qkv, ldq, out, ldo, positions, block_table, table_width, k_pool, v_pool, cos_t, sin_t, B, H, KV,
+                                          hd, page_size, scale, window, 0, n_splits, stream);
 }
 
 // ---------------------------------------------------------------------------- no allocation

@@ -31,7 +31,7 @@ attn_prefill_kernel(const bf16 *__restrict__ q, int ldq, bf16 *__restrict__ out,
                     const int *__restrict__ cu_rows, const int *__restrict__ seq_start,
                     const int *__restrict__ block_table, int table_width,
                     const bf16 *__restrict__ k_pool, const bf16 *__restrict__ v_pool,
-                    int KV, int G, float scale, int window) {
+                    int KV, int G, float scale, int window, int keep_first) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int TILE_BYTES = PAGE * HD * 2;
     constexpr int PF_ROWS = PF_WARPS * 16;
@@ -63,7 +63,13 @@ attn_prefill_kernel(const bf16 *__restrict__ q, int ldq, bf16 *__restrict__ out,
     // page range of the whole tile, and of this warp (to skip pages no row of the warp can see)
     const int tile_hi = start + q0 + tq - 1;
     const int tile_lo = (window > 0 && start + q0 - window + 1 > 0) ? start + q0 - window + 1 : 0;
-    const int p_begin = tile_lo / PAGE, p_end = tile_hi / PAGE + 1;
+    // Pages are walked by a running index: first the pages of the kept first keys that lie wholly in front of the
+    // first page any row's window reaches, then the pages up to the tile's last row; page_of gives the sequence's page.
+    const int keep = window > 0 ? keep_first : 0;
+    const int first_page = tile_lo / PAGE;
+    const int n_kept = min((keep + PAGE - 1) / PAGE, first_page);
+    const int p_begin = 0, p_end = n_kept + tile_hi / PAGE + 1 - first_page;
+    auto page_of = [&](int i) { return i < n_kept ? i : first_page + (i - n_kept); };
     int warp_hi = max(hi[0], hi[1]), warp_min_hi = min(hi[0], hi[1]), warp_max_lo = max(lo[0], lo[1]);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
@@ -93,7 +99,7 @@ attn_prefill_kernel(const bf16 *__restrict__ q, int ldq, bf16 *__restrict__ out,
     auto kaddr = [&](int st) { return s0 + st * 2 * TILE_BYTES; };
     auto vaddr = [&](int st) { return s0 + st * 2 * TILE_BYTES + TILE_BYTES; };
     {
-        size_t base = ((size_t)bt[p_begin] * KV + kvh) * PAGE * HD;
+        size_t base = ((size_t)bt[page_of(p_begin)] * KV + kvh) * PAGE * HD;
         load_page_cta<HD, PF_WARPS>(kaddr(0), k_pool + base, tid);
         load_page_cta<HD, PF_WARPS>(vaddr(0), v_pool + base, tid);
         cp_async_commit();
@@ -101,23 +107,24 @@ attn_prefill_kernel(const bf16 *__restrict__ q, int ldq, bf16 *__restrict__ out,
     for (int p = p_begin; p < p_end; p++) {
         const int st = (p - p_begin) & 1;
         if (p + 1 < p_end) {
-            size_t base = ((size_t)bt[p + 1] * KV + kvh) * PAGE * HD;
+            size_t base = ((size_t)bt[page_of(p + 1)] * KV + kvh) * PAGE * HD;
             load_page_cta<HD, PF_WARPS>(kaddr(st ^ 1), k_pool + base, tid);
             load_page_cta<HD, PF_WARPS>(vaddr(st ^ 1), v_pool + base, tid);
         }
         cp_async_commit();
         cp_async_wait<1>();                    // page p has landed (p + 1 may be in flight)
         __syncthreads();
-        if (p * PAGE <= warp_hi) {             // some row of this warp sees a key of the page
+        const int rp = page_of(p);
+        if (rp * PAGE <= warp_hi) {            // some row of this warp sees a key of the page
             float s[8][4];
 #pragma unroll
             for (int j = 0; j < 8; j++) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
             qk_page<HD>(s, qf, kaddr(st), lane);
             // only pages that hold a row's own position (or a window's edge) need the mask
-            if (p * PAGE + PAGE - 1 <= warp_min_hi && p * PAGE >= warp_max_lo)
-                softmax_update<HD / 8, false>(s, o, m, l, scale * LOG2E, p * PAGE, lo, hi, lane);
+            if (rp * PAGE + PAGE - 1 <= warp_min_hi && rp * PAGE >= warp_max_lo)
+                softmax_update<HD / 8, false>(s, o, m, l, scale * LOG2E, rp * PAGE, lo, hi, lane);
             else
-                softmax_update<HD / 8, true>(s, o, m, l, scale * LOG2E, p * PAGE, lo, hi, lane);
+                softmax_update<HD / 8, true>(s, o, m, l, scale * LOG2E, rp * PAGE, lo, hi, lane, keep);
             pv_page<HD>(o, s, vaddr(st), lane);
         }
         __syncthreads();                       // the stage is overwritten by the load after next
@@ -138,7 +145,7 @@ attn_prefill_kernel(const bf16 *__restrict__ q, int ldq, bf16 *__restrict__ out,
 template <int HD, int PF_WARPS>
 static int launch_prefill(const void *q, int ldq, void *out, int ldo, const int *cu_rows, const int *seq_start,
                           const int *block_table, int table_width, const void *k_pool, const void *v_pool,
-                          int n_seq, int max_new, int H, int KV, float scale, int window, cudaStream_t stream) {
+                          int n_seq, int max_new, int H, int KV, float scale, int window, int keep_first, cudaStream_t stream) {
     constexpr int smem = 2 * 2 * PAGE * HD * 2;
     static FgPerDevice configured;
     if (fg_needs_setup(configured)) {
@@ -148,20 +155,29 @@ static int launch_prefill(const void *q, int ldq, void *out, int ldo, const int 
     int G = H / KV, Gc = G < 16 ? G : 16, TQ = PF_WARPS * 16 / Gc;
     dim3 grid((max_new + TQ - 1) / TQ, KV * ((G + Gc - 1) / Gc), n_seq);
     return fg_launch(attn_prefill_kernel<HD, PF_WARPS>, grid, dim3(PF_WARPS * 32), (size_t)smem, stream, (const bf16 *)q, ldq, (bf16 *)out, ldo, cu_rows,
-        seq_start, block_table, table_width, (const bf16 *)k_pool, (const bf16 *)v_pool, KV, G, scale, window);
+        seq_start, block_table, table_width, (const bf16 *)k_pool, (const bf16 *)v_pool, KV, G, scale, window, keep_first);
 }
 
 // q: [rows, ldq] bf16 rows of all sequences one after another (cu_rows[b] = first row of sequence b,
 // seq_start[b] = its length before the step); pools [pages, KV, 64, HD] bf16; out [rows, ldo] bf16.
 // max_new: most rows any sequence brings.  Takes HD 64 and 128 and pages of 64.
+// keep_first (with a window): the first keep_first keys of a sequence stay visible to every row.
+extern "C" int fg_attention_prefill_kept(const void *q, int ldq, void *out, int ldo, const int *cu_rows,
+                                         const int *seq_start, const int *block_table, int table_width,
+                                         const void *k_pool, const void *v_pool, int n_seq, int max_new, int H, int KV,
+                                         int hd, int page_size, float scale, int window, int keep_first, cudaStream_t stream) {
+    if (n_seq <= 0 || max_new <= 0) return 0;
+    if (keep_first < 0 || page_size != PAGE || H % KV || n_seq > 65535 || ldq % 2 || ldo % 2 || ((uintptr_t)q & 3) || ((uintptr_t)out & 3))
+        return FG_ERR_BAD_SIZE;
+    if (hd == 64) return launch_prefill<64, 8>(q, ldq, out, ldo, cu_rows, seq_start, block_table, table_width, k_pool, v_pool, n_seq, max_new, H, KV, scale, window, keep_first, stream);
+    if (hd == 128) return launch_prefill<128, 4>(q, ldq, out, ldo, cu_rows, seq_start, block_table, table_width, k_pool, v_pool, n_seq, max_new, H, KV, scale, window, keep_first, stream);
+    return FG_ERR_BAD_SIZE;
+}
+
 extern "C" int fg_attention_prefill(const void *q, int ldq, void *out, int ldo, const int *cu_rows,
                                     const int *seq_start, const int *block_table, int table_width,
                                     const void *k_pool, const void *v_pool, int n_seq, int max_new, int H, int KV,
                                     int hd, int page_size, float scale, int window, cudaStream_t stream) {
-    if (n_seq <= 0 || max_new <= 0) return 0;
-    if (page_size != PAGE || H % KV || n_seq > 65535 || ldq % 2 || ldo % 2 || ((uintptr_t)q & 3) || ((uintptr_t)out & 3))
-        return FG_ERR_BAD_SIZE;
-    if (hd == 64) return launch_prefill<64, 8>(q, ldq, out, ldo, cu_rows, seq_start, block_table, table_width, k_pool, v_pool, n_seq, max_new, H, KV, scale, window, stream);
-    if (hd == 128) return launch_prefill<128, 4>(q, ldq, out, ldo, cu_rows, seq_start, block_table, table_width, k_pool, v_pool, n_seq, max_new, H, KV, scale, window, stream);
-    return FG_ERR_BAD_SIZE;
+    return fg_attention_prefill_kept(q, ldq, out, ldo, cu_rows, seq_start, block_table, table_width, k_pool, v_pool, n_seq, max_new, H,
+                                     KV, hd, page_size, scale, window, 0, stream);
 }

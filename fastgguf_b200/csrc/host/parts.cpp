@@ -219,12 +219,11 @@ int decode_splits(int n_sm, int n_seq, int n_heads, int n_kv_heads, int table_wi
     return s;
 }
 
-// The tensor-core attention kernels take bfloat16, head size 64 / 128 for keys and values alike, pages of 64, and a
-// plain window; kept first keys and other sizes go to the any-size kernel.
+// The tensor-core attention kernels take bfloat16, head size 64 / 128 for keys and values alike and pages of 64; other
+// sizes go to the any-size kernel.  Kept first keys: the mma.sync kernels walk their pages in front of the window's.
 static bool fast_attention_ok(const Runtime &rt, const Tensor &q, const LayerIO &io, const AttentionShape &a) {
     return !rt.plain_kernels && q.dtype == FG_BF16 && io.cache_dtype == FG_BF16 && (a.head_dim == 64 || a.head_dim == 128) &&
-           a.v_head_dim == a.head_dim && !(a.window > 0 && a.keep_first > 0) && io.page_size == 64 && q.ld % 2 == 0 &&
-           ((uintptr_t)q.data % 4) == 0;
+           a.v_head_dim == a.head_dim && io.page_size == 64 && q.ld % 2 == 0 && ((uintptr_t)q.data % 4) == 0;
 }
 
 static Tensor attention(Runtime &rt, const Tensor &q, const Batch &b, const LayerIO &io, const AttentionShape &a) {
@@ -239,20 +238,23 @@ static Tensor attention(Runtime &rt, const Tensor &q, const Batch &b, const Laye
                 part_o = (float *)rt.arena->alloc((size_t)b.n_seq * H * n_splits * hd * sizeof(float));
                 part_ml = (float *)rt.arena->alloc((size_t)b.n_seq * H * n_splits * 2 * sizeof(float));
             }
-            FG_LAUNCH("attn", fg_attention_decode, q.data, (int)q.ld, out.data, (int)out.ld, b.positions, table, b.table_width,
-                      io.k_pool, io.v_pool, b.n_seq, H, KV, hd, io.page_size, a.scale, a.window, n_splits, part_o, part_ml, rt.stream);
+            FG_LAUNCH("attn", fg_attention_decode_kept, q.data, (int)q.ld, out.data, (int)out.ld, b.positions, table, b.table_width,
+                      io.k_pool, io.v_pool, b.n_seq, H, KV, hd, io.page_size, a.scale, a.window, a.keep_first, n_splits, part_o, part_ml,
+                      rt.stream);
             return out;
         }
         // Many new tokens: 128-row tiles on the tcgen05 tensor cores.  A few rows (a sequence fed in short
         // pieces) waste less of the mma.sync kernel's 64-row tile.
-        bool tc = b.max_new * (H / KV) >= 64 && q.ld % 8 == 0 && ((uintptr_t)q.data % 16) == 0;
+        // The tcgen05 kernel knows a plain window only; with kept first keys every portion takes the mma.sync kernel.
+        bool tc = b.max_new * (H / KV) >= 64 && q.ld % 8 == 0 && ((uintptr_t)q.data % 16) == 0 && !(a.window > 0 && a.keep_first > 0);
         if (tc)
             FG_LAUNCH("attn", fg_attention_prefill_tc, q.data, (int)q.ld, out.data, (int)out.ld, b.cu_rows, b.seq_start, table,
                       b.table_width, io.k_pool, io.v_pool, io.n_pages, b.n_seq, b.max_new, H, KV, hd, io.page_size, a.scale, a.window,
                       rt.stream);
         else
-            FG_LAUNCH("attn", fg_attention_prefill, q.data, (int)q.ld, out.data, (int)out.ld, b.cu_rows, b.seq_start, table,
-                      b.table_width, io.k_pool, io.v_pool, b.n_seq, b.max_new, H, KV, hd, io.page_size, a.scale, a.window, rt.stream);
+            FG_LAUNCH("attn", fg_attention_prefill_kept, q.data, (int)q.ld, out.data, (int)out.ld, b.cu_rows, b.seq_start, table,
+                      b.table_width, io.k_pool, io.v_pool, b.n_seq, b.max_new, H, KV, hd, io.page_size, a.scale, a.window, a.keep_first,
+                      rt.stream);
         return out;
     }
     if (q.dtype != io.cache_dtype) fail(FG_E_INTERNAL, "attention: q and the cache must share a dtype");
@@ -278,9 +280,9 @@ Tensor rope_attention(Runtime &rt, const Tensor &qkv, const Batch &b, const Laye
         int n_splits = decode_splits(rt.n_sm, b.n_seq, H, KV, b.table_width, hd);
         if (n_splits == 1 || n_splits == 2 || n_splits == 4 || n_splits == 8) {
             Tensor out = rt.arena->matrix(qkv.rows, (int64_t)H * hd, FG_BF16);
-            FG_LAUNCH("attn", fg_attention_decode_fused, qkv.data, (int)qkv.ld, out.data, (int)out.ld, b.positions, table,
-                      b.table_width, io.k_pool, io.v_pool, cos_t, sin_t, b.n_seq, H, KV, hd, io.page_size, a.scale, a.window, n_splits,
-                      rt.stream);
+            FG_LAUNCH("attn", fg_attention_decode_fused_kept, qkv.data, (int)qkv.ld, out.data, (int)out.ld, b.positions, table,
+                      b.table_width, io.k_pool, io.v_pool, cos_t, sin_t, b.n_seq, H, KV, hd, io.page_size, a.scale, a.window,
+                      a.keep_first, n_splits, rt.stream);
             return out;
         }
     }

@@ -132,6 +132,12 @@ MIXERS = {
     "attention, window and kept keys": attention(3, 3, 32, 8, 0.2, size=7, keep_first=3),
     "attention, more kept keys than window": attention(2, 1, 40, 24, 0.2, size=2, keep_first=11),
     "attention, window of one": attention(2, 2, 16, 16, 0.5, size=1, keep_first=1),
+    # head sizes of the tensor-core kernels, sequences of several pages: kept keys on one page and on two, in front of
+    # the window's pages and overlapping them
+    "long attention, head 64, kept keys on two pages": attention(4, 2, 64, 64, 0.125, size=20, keep_first=70),
+    "long attention, head 128, kept keys and a wide window": attention(6, 1, 128, 128, 0.09, size=100, keep_first=5),
+    "long attention, head 64, window alone": attention(2, 1, 64, 64, 0.125, size=65),
+    "long retention, head 128": retention(2, 128, 128, [0.999, 0.99], rot=(10000.0, 64)),
 }
 
 
@@ -139,33 +145,36 @@ MIXERS = {
 @pytest.mark.parametrize("name", list(MIXERS))
 def test_mixer_alone(tmp_path, name, dtype):
     """One layer of a mixer alone (norm, mixer, norm, residual add) on rows given by the test: a portion of 37 rows,
-    then one of 2, then single rows, so the second and later calls start from what the first left behind."""
+    then one of 2, then single rows, so the second and later calls start from what the first left behind (the long
+    cases: 160, 30 and 2 rows, then 38 single ones)."""
     cfg = one_layer(MIXERS[name])
     d, W = make_model(tmp_path, cfg, 7, sharp=2.0)
     eng = engine_for(d, dtype)
     g = torch.Generator().manual_seed(8)
-    x = torch.randn(45, cfg["width"], generator=g, dtype=torch.float64)
+    cuts = [160, 30, 2] + [1] * 38 if name.startswith("long") else [37, 2, 1, 1, 1, 1, 1, 1]
+    T = sum(cuts)
+    x = torch.randn(T, cfg["width"], generator=g, dtype=torch.float64)
     # the plain layer, whole
     layer, mc = cfg["layers"][0], cfg["layers"][0]["mixer"]
     h = pz.offset_norm(x, W["l0.norm1"], 1e-5)
-    pos = torch.arange(45)
+    pos = torch.arange(T)
     if layer["type"] == "retention":
         y = pz.retention_mixer(h, pos, W, "l0.mix.", mc, 1e-5, torch.zeros(mc["heads"], mc["dim"], mc["vdim"], dtype=torch.float64))
     else:
         full = mc
-        keys = (h @ W["l0.mix.k"].T).reshape(45, mc["kv_heads"], mc["dim"])
-        values = (h @ W["l0.mix.v"].T).reshape(45, mc["kv_heads"], mc["vdim"])
+        keys = (h @ W["l0.mix.k"].T).reshape(T, mc["kv_heads"], mc["dim"])
+        values = (h @ W["l0.mix.v"].T).reshape(T, mc["kv_heads"], mc["vdim"])
         y = pz.attention_mixer(h, pos, W, "l0.mix.", full, keys, values)
     want = (x + pz.offset_norm(y, W["l0.norm1b"], 1e-5)).numpy()
     slot = eng.acquire()
     got, at = [], 0
-    for n in [37, 2, 1, 1, 1, 1, 1, 1]:
+    for n in cuts:
         part = np.ascontiguousarray(x[at:at + n].numpy(), dtype=np.float32)
         got.append(eng.block_forward(0, [(slot, n)], part))
         at += n
     got = np.concatenate(got)
     tol = 5e-6 if dtype == "float32" else 4e-2
-    for r in range(45):
+    for r in range(T):
         assert rel_err(got[r], want[r]) < tol, (name, r)
 
 
