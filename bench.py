@@ -3,6 +3,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--model 1b|3b|8b] [--dtype bfloat16|float32]
                     [--layers L] [--no-points] [--no-prefill] [--impl reference]
+    python bench.py --compare zirivik [--sizes s,m] [--steps K] [--warmup W] [--batch 8]
 
 Default run: the layer sizes of Llama 3.2 1B with random weights, bfloat16, a batch of 8 sequences with random
 prompts of unequal lengths 128..1024, context 4096.  ``--model 3b``: prompts 64..2048, context 4096; ``--model 8b``:
@@ -13,6 +14,11 @@ lists in and out; ``prefill`` is one step of 2,048 prompt tokens; ``roofline`` d
 read (every weight once, the cache of the live requests) by its time; ``points`` holds decode at batch 1 and 64, and
 at the headline batch with the reference's default sampler instead of greedy; ``points_detail`` what each of them was
 made of.  Every step reads gigabytes of weights, far more than the 126 MB L2, so no flush is needed between timed steps.
+
+``--compare zirivik`` leaves all of that alone and prints another line: prefill (one step of 2,048 tokens) and decode
+(graph-replayed steps of a batch) of Zirivik models whose layers have the sizes of real models, beside Llama models
+of the same width, depth, heads and feed-forward size, with the device time of every launcher of one prefill step and
+of decode steps run eagerly (``profile``), so that like kernels can be set side by side.
 """
 import argparse
 import json
@@ -124,6 +130,105 @@ def prefill_flops(c, layers, T):
     return layers * (gemm + attn) + 2 * c["vocab_size"] * E
 
 
+def zirivik_config(width, heads, kv_heads, head_dim, ff, vocab, window, expert_ff, blocks=2):
+    """Layers of a real model's sizes in the design's own pattern: retention + dense, retention + experts, attention +
+    dense, attention on the layer before's keys and values + experts; `blocks` times."""
+    ret = {"heads": width // 128, "dim": 128, "vdim": 128, "decay": [1.0 - 2.0 ** (-5 - 6 * h / max(1, width // 128 - 1)) for h in range(width // 128)],
+           "rot": {"base": 1000000.0, "dims": 64}}
+    att = {"heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim, "scale": head_dim ** -0.5,
+           "mask": {"size": window, "keep_first": 4}}
+    dense = {"kind": "dense", "ff": ff}
+    moe = {"kind": "moe", "expert": {"ff": expert_ff, "limit": 7.0}, "router": {"experts": 8, "top": 2}}
+    layers = []
+    for _ in range(blocks):
+        at = len(layers) + 2
+        layers += [{"type": "retention", "mixer": ret, "mlp": dense}, {"type": "retention", "mixer": ret, "mlp": moe},
+                   {"type": "attention", "mixer": att, "mlp": dense}, {"type": "attention", "mixer": dict(att, kv_from=at), "mlp": moe}]
+    return {"architecture": "Zirivik", "vocab": vocab, "width": width, "embedding": {"scale": width ** 0.5}, "norm": {"eps": 1e-6},
+            "logit_softcap": 30.0, "layers": layers}
+
+
+#: name -> (width, heads, kv_heads, head_dim, ff, vocab, window, expert_ff)
+COMPARE_SIZES = {"s": (2048, 32, 8, 64, 8192, 32768, 1024, 2048), "m": (4096, 32, 8, 128, 14336, 32768, 2048, 4096)}
+
+
+def compare_zirivik(args):
+    import numpy as np
+    import torch
+    from fastgguf_b200.engine.api import Engine
+    from fastgguf_b200.engine.batch import StepEntry
+    from fastgguf_b200.registry import config_from_dict
+    from fastgguf_b200.sampling import SamplingParams
+    W, K, B = max(3, args.warmup), args.steps, args.batch
+    rng = np.random.default_rng(0)
+    out = {"compare": "zirivik", "dtype": args.dtype, "batch": B, "prefill_tokens": PREFILL_TOKENS, "steps": K, "warmup": W,
+           "peaks": peaks(), "sizes": {}}
+    for name in args.sizes.split(","):
+        width, heads, kv, hd, ff, vocab, window, eff = COMPARE_SIZES[name]
+        z = zirivik_config(width, heads, kv, hd, ff, vocab, window, eff)
+        llama = dict(LLAMA_3_2_1B, hidden_size=width, num_hidden_layers=len(z["layers"]), num_attention_heads=heads,
+                     num_key_value_heads=kv, head_dim=hd, intermediate_size=ff, vocab_size=vocab, rope_scaling=None, bos_token_id=1, eos_token_id=2)
+        row = {}
+        for label, cd in (("zirivik", z), ("llama", llama)):
+            cfg = config_from_dict(cd)
+            per_seq = (1024 + W + K * 3 + 128 + 63) // 64 * 64
+            engine = Engine.from_random(cfg, 0, dtype=args.dtype, max_tokens=max(B * per_seq, PREFILL_TOKENS + 64) + 64 * B,
+                                        max_batch=B, max_seq_len=4096)
+            stream = torch.cuda.ExternalStream(engine.stream)
+            toks = rng.integers(0, vocab, size=PREFILL_TOKENS).tolist()
+
+            def prefill_once():
+                slot = engine.acquire()
+                t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                engine.check_device()
+                t0.record(stream)
+                engine.step_host([StepEntry(slot, toks, [PREFILL_TOKENS - 1])])
+                t1.record(stream)
+                t1.synchronize()
+                engine.release(slot)
+                return t0.elapsed_time(t1)
+            times = [prefill_once() for _ in range(3 + 5)][3:]
+            pms = sorted(times)[len(times) // 2]
+            prompts = [rng.integers(0, vocab, size=int(L)).tolist() for L in rng.integers(256, 1025, size=B)]
+            session = engine.session(prompts, SamplingParams(temp=0.0))
+            live = list(range(B))
+            for _ in range(W):
+                session.advance(live)
+            engine.check_device()
+            dts = []
+            for _ in range(3):
+                t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                t0.record(stream)
+                for _ in range(K):
+                    session.advance(live)
+                t1.record(stream)
+                t1.synchronize()
+                dts.append(t0.elapsed_time(t1) / K)
+            engine.check_device()
+            launches = session.launches_per_step
+            session.close()
+            dms = sorted(dts)[1]
+            # per-launcher device times: one prefill step, then decode steps run eagerly
+            engine.profile(True)
+            prefill_once()
+            prof_prefill = engine.profile_report()
+            engine.generate(prompts, temp=0, max_tokens=9, ignore_eos=True)
+            prof_all = engine.profile_report()
+            engine.profile(False)
+            row[label] = {"parameters": cfg.describe()["parameters"], "layers": len(z["layers"]),
+                          "prefill_ms": round(pms, 3), "prefill_tokens_per_s": round(PREFILL_TOKENS / (pms * 1e-3), 1),
+                          "decode_ms_per_step": round(dms, 4), "decode_tokens_per_s": round(B * 1000.0 / dms, 1),
+                          "launches_per_decode_step": launches,
+                          "profile_prefill": [{"name": r["name"], "calls": r["calls"], "ms": round(r["ms"], 4)} for r in prof_prefill[:16]],
+                          "profile_prompt_and_8_decode_steps": [{"name": r["name"], "calls": r["calls"], "ms": round(r["ms"], 4)}
+                                                               for r in prof_all[:24]]}
+            del engine
+        row["config"] = {"width": width, "heads": heads, "kv_heads": kv, "head_dim": hd, "ff": ff, "vocab": vocab, "window": window,
+                         "experts": "8 of ff %d, 2 a row" % eff, "retention": "%d heads of 128 x 128" % (width // 128)}
+        out["sizes"][name] = row
+    return out
+
+
 def reference_arm(args):
     """The reference has no installer and no GPU path; see baseline/reference_arm.py for what can be run of it."""
     try:
@@ -149,6 +254,9 @@ def main():
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points")
     ap.add_argument("--no-prefill", action="store_true", help="skip the prefill measurement")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end measurement")
+    ap.add_argument("--compare", default=None, choices=["zirivik"],
+                    help="another line instead of the default one: this design beside Llama at equal sizes, prefill and decode")
+    ap.add_argument("--sizes", default="s", help="with --compare: which sizes, of " + ",".join(sorted(COMPARE_SIZES)))
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -157,6 +265,14 @@ def main():
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
+    if args.compare:
+        if any(n not in COMPARE_SIZES for n in args.sizes.split(",")):
+            print("bench.py: --sizes takes " + ",".join(sorted(COMPARE_SIZES)))
+            return 2
+        if args.steps == 256:
+            args.steps = 64
+        print(json.dumps(compare_zirivik(args)))
+        return 0
 
     import numpy as np
     import torch

@@ -288,44 +288,71 @@ extern "C" int fg_kv_append(const void *qkv, int dtype, int ld, int k_off, const
 // For blocks that normalise a sublayer's output before adding it: x[m] += t[m] / rms(t[m]) * w_post, and,
 // when w_next is given, out[m] = x[m] / rms(x[m]) * w_next for the sublayer that reads x next - one pass over
 // the row instead of three kernels.  Statistics and the sum are 32-bit; one block a row, fixed reduction order.
-template <typename TO>
+// VEC: rows are read and written four elements at a time (E % 4 == 0, 16-byte aligned rows)
+template <typename TO, bool VEC>
 __global__ void norm_add_norm_kernel(const float *__restrict__ t, const float *__restrict__ w_post, float *__restrict__ x,
                                      const float *__restrict__ w_next, TO *__restrict__ out, int E, float eps_post,
                                      float eps_next) {
     __shared__ float scratch[32];
-    extern __shared__ float row[];        // [E] the updated residual row, when a next norm is wanted
+    extern __shared__ __align__(16) float row[];        // [E] the updated residual row, when a next norm is wanted
     pdl_launch_dependents();
     pdl_wait();
     const size_t base = (size_t)blockIdx.x * E;
     float ss = 0.f;
-    for (int i = threadIdx.x; i < E; i += blockDim.x) { float v = t[base + i]; ss += v * v; }
+    if (VEC) {
+        const float4 *t4 = (const float4 *)(t + base);
+        for (int i = threadIdx.x; i < E / 4; i += blockDim.x) { float4 v = t4[i]; ss += v.x * v.x; ss += v.y * v.y; ss += v.z * v.z; ss += v.w * v.w; }
+    } else {
+        for (int i = threadIdx.x; i < E; i += blockDim.x) { float v = t[base + i]; ss += v * v; }
+    }
     ss = block_sum(ss, scratch);
     const float inv = 1.0f / sqrtf(ss / (float)E + eps_post);
     float ss2 = 0.f;
-    for (int i = threadIdx.x; i < E; i += blockDim.x) {
-        float v = x[base + i] + t[base + i] * inv * w_post[i];
-        x[base + i] = v;
-        if (w_next) { row[i] = v; ss2 += v * v; }
+    if (VEC) {
+        const float4 *t4 = (const float4 *)(t + base), *w4 = (const float4 *)w_post;
+        float4 *x4 = (float4 *)(x + base), *r4 = (float4 *)row;
+        for (int i = threadIdx.x; i < E / 4; i += blockDim.x) {
+            float4 a = t4[i], g = w4[i], v = x4[i];
+            v.x += a.x * inv * g.x; v.y += a.y * inv * g.y; v.z += a.z * inv * g.z; v.w += a.w * inv * g.w;
+            x4[i] = v;
+            if (w_next) { r4[i] = v; ss2 += v.x * v.x; ss2 += v.y * v.y; ss2 += v.z * v.z; ss2 += v.w * v.w; }
+        }
+    } else {
+        for (int i = threadIdx.x; i < E; i += blockDim.x) {
+            float v = x[base + i] + t[base + i] * inv * w_post[i];
+            x[base + i] = v;
+            if (w_next) { row[i] = v; ss2 += v * v; }
+        }
     }
     if (!w_next) return;
     ss2 = block_sum(ss2, scratch);
     const float inv2 = 1.0f / sqrtf(ss2 / (float)E + eps_next);
-    for (int i = threadIdx.x; i < E; i += blockDim.x) out[base + i] = from_f32<TO>(row[i] * inv2 * w_next[i]);
+    if (VEC) {
+        const float4 *r4 = (const float4 *)row, *w4 = (const float4 *)w_next;
+        for (int i = threadIdx.x; i < E / 4; i += blockDim.x) {
+            float4 v = r4[i], g = w4[i];
+            store4<TO>(out + base + 4 * i, v.x * inv2 * g.x, v.y * inv2 * g.y, v.z * inv2 * g.z, v.w * inv2 * g.w);
+        }
+    } else {
+        for (int i = threadIdx.x; i < E; i += blockDim.x) out[base + i] = from_f32<TO>(row[i] * inv2 * w_next[i]);
+    }
 }
 
 extern "C" int fg_norm_add_norm(const float *t, const float *w_post, float *x, const float *w_next, void *out, int out_dtype,
                                 int M, int E, float eps_post, float eps_next, cudaStream_t stream) {
     if (M <= 0) return 0;
-    int threads = E >= 2048 ? 256 : (E >= 512 ? 128 : 64);
     size_t smem = w_next ? (size_t)E * sizeof(float) : 0;
     if (smem > 48 * 1024) return FG_ERR_BAD_SIZE;
-    if (out_dtype == FG_F32 || !w_next)
-        return fg_launch(norm_add_norm_kernel<float>, dim3(M), dim3(threads), smem, stream, t, w_post, x, w_next, (float *)out, E,
-                         eps_post, eps_next);
-    if (out_dtype == FG_BF16)
-        return fg_launch(norm_add_norm_kernel<bf16>, dim3(M), dim3(threads), smem, stream, t, w_post, x, w_next, (bf16 *)out, E,
-                         eps_post, eps_next);
-    return FG_ERR_BAD_DTYPE;
+    const bool vec = E % 4 == 0 && ((((uintptr_t)t) | ((uintptr_t)w_post) | ((uintptr_t)x) | ((uintptr_t)w_next) | ((uintptr_t)out)) & 15) == 0;
+    int per = vec ? E / 4 : E;
+    int threads = per >= 1024 ? 256 : (per >= 256 ? 128 : 64);
+    const bool wide = out_dtype == FG_F32 || !w_next;
+    if (!wide && out_dtype != FG_BF16) return FG_ERR_BAD_DTYPE;
+#define NAN_LAUNCH(TO, VEC) fg_launch(norm_add_norm_kernel<TO, VEC>, dim3(M), dim3(threads), smem, stream, t, w_post, x, w_next, (TO *)out, E, \
+                                      eps_post, eps_next)
+    if (wide) return vec ? NAN_LAUNCH(float, true) : NAN_LAUNCH(float, false);
+    return vec ? NAN_LAUNCH(bf16, true) : NAN_LAUNCH(bf16, false);
+#undef NAN_LAUNCH
 }
 
 // ------------------------------------------------------------------ activations in place

@@ -9,7 +9,8 @@
 // Layout.  A "pair" p = row * top + k is a row's k-th choice.  route() writes the pair's expert and weight and groups
 // pairs by expert: `order[slot] = pair`, `slot_of[pair] = slot`, expert e owning slots [offsets[e], offsets[e + 1]).
 // The contractions run over slots, so that a tile of rows shares one expert's weights; all sizes that depend on the
-// routing stay on the device (nothing is read back).  An output element is summed along k in the same order whichever
+// routing stay on the device (only the per-expert path of long portions, at the end of this file, has the host read the
+// experts' row counts).  An output element is summed along k in the same order whichever
 // tile or slot its row lands in, and a row's experts are added in the order of its choices, so a row's result does not
 // depend on what else is in the step.
 //
@@ -19,6 +20,68 @@
 
 #define MOE_MAX_EXPERTS 256
 #define MOE_MAX_TOP 8
+
+// ------------------------------------------------------------------ router logits
+// z[m, e] = x[m] . W[e], float32 accumulation of the inputs as they are.  A block per row: every thread takes runs of
+// 16 bytes of the row and of each expert's weights (the router's few rows stay in cache), eight experts at a time; the
+// threads' sums are added in a fixed order.  (The general contraction kernel spends a 64-wide tile on these few outputs.)
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_logits_kernel(const T *__restrict__ x, int ldx, const T *__restrict__ W, int ldw, float *__restrict__ z, int X, int E, int vec) {
+    __shared__ float part[8][8];
+    pdl_launch_dependents();
+    pdl_wait();
+    constexpr int VEC = 16 / (int)sizeof(T);
+    const int m = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const T *xr = x + (size_t)m * ldx;
+    for (int e0 = 0; e0 < X; e0 += 8) {
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        if (vec) {
+            for (int k = threadIdx.x * VEC; k < E; k += 256 * VEC) {
+                const uint4 xv = *(const uint4 *)(xr + k);
+                const T *xe = (const T *)&xv;
+#pragma unroll
+                for (int u = 0; u < 8; u++) {
+                    if (e0 + u >= X) break;
+                    const uint4 wv = *(const uint4 *)(W + (size_t)(e0 + u) * ldw + k);
+                    const T *we = (const T *)&wv;
+#pragma unroll
+                    for (int i = 0; i < VEC; i++) acc[u] = fmaf(to_f32<T>(xe[i]), to_f32<T>(we[i]), acc[u]);
+                }
+            }
+        } else {
+            for (int k = threadIdx.x; k < E; k += 256) {
+                const float xv = to_f32<T>(xr[k]);
+#pragma unroll
+                for (int u = 0; u < 8; u++)
+                    if (e0 + u < X) acc[u] = fmaf(xv, to_f32<T>(W[(size_t)(e0 + u) * ldw + k]), acc[u]);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            float v = warp_sum(acc[u]);
+            if (lane == 0) part[warp][u] = v;
+        }
+        __syncthreads();
+        if (threadIdx.x < 8 && e0 + threadIdx.x < X) {
+            float v = 0.f;
+            for (int w = 0; w < 8; w++) v += part[w][threadIdx.x];
+            z[(size_t)m * X + e0 + threadIdx.x] = v;
+        }
+        __syncthreads();
+    }
+}
+
+extern "C" int fg_moe_logits(const void *x, int ldx, const void *W, int ldw, int dtype, float *z, int M, int X, int E, cudaStream_t stream) {
+    if (M <= 0) return 0;
+    const int per = dtype == FG_F32 ? 4 : 8;
+    const int vec = E % per == 0 && ldx % per == 0 && ldw % per == 0 && ((((uintptr_t)x) | ((uintptr_t)W)) & 15) == 0;
+    if (dtype == FG_F32)
+        return fg_launch(moe_logits_kernel<float>, dim3(M), dim3(256), 0, stream, (const float *)x, ldx, (const float *)W, ldw, z, X, E, vec);
+    if (dtype == FG_BF16)
+        return fg_launch(moe_logits_kernel<bf16>, dim3(M), dim3(256), 0, stream, (const bf16 *)x, ldx, (const bf16 *)W, ldw, z, X, E, vec);
+    return FG_ERR_BAD_DTYPE;
+}
 
 // ------------------------------------------------------------------ routing
 // One block.  logits: [M, X] float32.
@@ -168,12 +231,29 @@ moe_rows_kernel(const T *__restrict__ A, int lda, const T *__restrict__ W, void 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const T *We = W + (size_t)e * (FIRST ? 2 : 1) * N * K;
     const float w = FIRST ? pair_weight[pair] : 1.0f;
+    constexpr int VEC = 16 / (int)sizeof(T);         // elements a 16-byte load brings
+    const bool vec = (K % VEC) == 0 && (((uintptr_t)W) & 15) == 0;
     for (int n = blockIdx.x * 8 + warp; n < N; n += gridDim.x * 8) {
         const T *g = We + (size_t)n * K, *u = We + (size_t)(N + n) * K;
         float sg = 0.f, su = 0.f;
-        for (int k = lane; k < K; k += 32) {
-            sg = fmaf(xs[k], to_f32<T>(g[k]), sg);
-            if (FIRST) su = fmaf(xs[k], to_f32<T>(u[k]), su);
+        if (vec) {
+            for (int k = lane * VEC; k < K; k += 32 * VEC) {
+                const uint4 gv = *(const uint4 *)(g + k);
+                const T *ge = (const T *)&gv;
+#pragma unroll
+                for (int i = 0; i < VEC; i++) sg = fmaf(xs[k + i], to_f32<T>(ge[i]), sg);
+                if (FIRST) {
+                    const uint4 uv = *(const uint4 *)(u + k);
+                    const T *ue = (const T *)&uv;
+#pragma unroll
+                    for (int i = 0; i < VEC; i++) su = fmaf(xs[k + i], to_f32<T>(ue[i]), su);
+                }
+            }
+        } else {
+            for (int k = lane; k < K; k += 32) {
+                sg = fmaf(xs[k], to_f32<T>(g[k]), sg);
+                if (FIRST) su = fmaf(xs[k], to_f32<T>(u[k]), su);
+            }
         }
         sg = warp_sum(sg);
         if (FIRST) su = warp_sum(su);
@@ -229,6 +309,50 @@ extern "C" int fg_moe_second(const void *y, int ldy, const void *w_out, float *o
                          ldo, offsets, order, (const float *)nullptr, X, top, E, F, 0.f, 0.f);
     return fg_launch(moe_tile_kernel<bf16, false>, grid, dim3(256), 0, stream, (const bf16 *)y, ldy, (const bf16 *)w_out, (void *)out, ldo,
                      offsets, order, (const float *)nullptr, X, top, E, F, 0.f, 0.f);
+}
+
+// ------------------------------------------------------------------ long portions: the experts' contractions as plain ones
+// With the rows of each expert side by side (xs[slot] = x[order[slot] / top]) an expert's contraction is an ordinary one
+// over its run of slots, which the engine's tensor-core kernels take; these two kernels are what is left around them.
+template <typename T>
+__global__ void moe_gather_kernel(const T *__restrict__ x, int ldx, const int *__restrict__ order, int top, T *__restrict__ xs, int E) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int slot = blockIdx.x;
+    const T *src = x + (size_t)(order[slot] / top) * ldx;
+    T *dst = xs + (size_t)slot * E;
+    if (sizeof(T) == 2 && (E & 7) == 0 && (ldx & 7) == 0 && (((uintptr_t)x | (uintptr_t)xs) & 15) == 0) {
+        for (int i = threadIdx.x; i < E / 8; i += blockDim.x) ((uint4 *)dst)[i] = ((const uint4 *)src)[i];
+    } else {
+        for (int i = threadIdx.x; i < E; i += blockDim.x) dst[i] = src[i];
+    }
+}
+
+extern "C" int fg_moe_gather(const void *x, int ldx, int dtype, const int *order, int top, void *xs, int P, int E, cudaStream_t stream) {
+    if (P <= 0) return 0;
+    if (dtype == FG_F32) return fg_launch(moe_gather_kernel<float>, dim3(P), dim3(128), 0, stream, (const float *)x, ldx, order, top, (float *)xs, E);
+    if (dtype == FG_BF16) return fg_launch(moe_gather_kernel<bf16>, dim3(P), dim3(128), 0, stream, (const bf16 *)x, ldx, order, top, (bf16 *)xs, E);
+    return FG_ERR_BAD_DTYPE;
+}
+
+// gu: [P, 2F] float32 (gate | up) of each slot -> y[P, F] = act(w gate, w up), w the slot's routing weight
+template <typename T>
+__global__ void moe_act_kernel(const float *__restrict__ gu, const int *__restrict__ order, const float *__restrict__ pair_weight,
+                               T *__restrict__ y, int F, float limit, float alpha) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int slot = blockIdx.x;
+    const float w = pair_weight[order[slot]];
+    const float *g = gu + (size_t)slot * 2 * F, *u = g + F;
+    for (int i = threadIdx.x; i < F; i += blockDim.x) y[(size_t)slot * F + i] = from_f32<T>(expert_act(w * g[i], w * u[i], limit, alpha));
+}
+
+extern "C" int fg_moe_act(const float *gu, const int *order, const float *pair_weight, void *y, int dtype, int P, int F, float limit,
+                          float alpha, cudaStream_t stream) {
+    if (P <= 0) return 0;
+    if (dtype == FG_F32) return fg_launch(moe_act_kernel<float>, dim3(P), dim3(256), 0, stream, gu, order, pair_weight, (float *)y, F, limit, alpha);
+    if (dtype == FG_BF16) return fg_launch(moe_act_kernel<bf16>, dim3(P), dim3(256), 0, stream, gu, order, pair_weight, (bf16 *)y, F, limit, alpha);
+    return FG_ERR_BAD_DTYPE;
 }
 
 // ------------------------------------------------------------------ sum of a row's experts, in the order of its choices

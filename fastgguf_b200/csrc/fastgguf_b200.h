@@ -68,6 +68,10 @@ int fg_retention_chunked(const float *proj, int ld, void *out, int out_dtype, in
                          const int *cu_rows, const int *slots, const float *cos_t, const float *sin_t,
                          const float *decay, float *state, int *plan, float *U, int n_seq, int n_chunks, int H, int dk,
                          int dv, float k_scale, float eps, cudaStream_t stream);
+int fg_moe_logits(const void *x, int ldx, const void *W, int ldw, int dtype, float *z, int M, int X, int E, cudaStream_t stream);
+int fg_moe_gather(const void *x, int ldx, int dtype, const int *order, int top, void *xs, int P, int E, cudaStream_t stream);
+int fg_moe_act(const float *gu, const int *order, const float *pair_weight, void *y, int dtype, int P, int F, float limit,
+               float alpha, cudaStream_t stream);
 int fg_moe_route(const float *logits, int M, int X, int top, int *pair_expert, float *pair_weight, int *offsets, int *order,
                  int *slot_of, cudaStream_t stream);
 int fg_moe_first(const void *x, int ldx, const void *w_in, void *y, int ldy, int dtype, const int *pair_expert,

@@ -524,6 +524,7 @@ public:
         return true;
     }
     bool supports_deferred_norm() const override { return true; }
+    bool can_overwrite() const override { return true; }
     void load(const std::map<std::string, Weight> &tensors, Runtime &rt) override {
         o_ = Linear(tensor_of(tensors, "o_proj.weight"));
         if (queries_only_) {
@@ -568,7 +569,7 @@ public:
         shape.window = window_; shape.keep_first = window_ > 0 ? keep_first_ : 0; shape.rotate = rotate_;
         Tensor attn = rope_attention(rt, qkv, batch, io, position_->cos_table(), position_->sin_table(), shape);
         DeferredNorm started;
-        o_.forward(rt, attn, nullptr, residual, FG_F32, true, emit_norm, &started);
+        o_.forward(rt, attn, nullptr, residual, FG_F32, !rt.overwrite, emit_norm, &started);
         return started;
     }
 
@@ -593,6 +594,7 @@ public:
         return {{"gate_proj.weight", {F_, E_}}, {"up_proj.weight", {F_, E_}}, {"down_proj.weight", {E_, F_}}};
     }
     bool supports_deferred_norm() const override { return true; }
+    bool can_overwrite() const override { return true; }
     void load(const std::map<std::string, Weight> &tensors, Runtime &rt) override {
         const Weight &g = tensor_of(tensors, "gate_proj.weight"), &u = tensor_of(tensors, "up_proj.weight");
         int dt = g.t.dtype == u.t.dtype ? g.t.dtype : FG_F32;
@@ -621,7 +623,7 @@ public:
             if (gu.rows > 0) FG_LAUNCH("core", fg_silu_mul, gu.data, t.data, gu.dtype, (int)gu.rows, F_, rt.stream);
         }
         DeferredNorm started;
-        down_.forward(rt, t, nullptr, residual, FG_F32, true, emit_norm, &started);
+        down_.forward(rt, t, nullptr, residual, FG_F32, !rt.overwrite, emit_norm, &started);
         return started;
     }
 
@@ -699,7 +701,11 @@ public:
         const int M = (int)x.rows, E = (int)x.cols;
         Tensor xn = !pending.defined() ? mixer_norm->forward(rt, x, nullptr, 0) : pending.tiles == 0 ? pending.xw : pending.materialize(rt);
         Tensor t = rt.arena->matrix(M, E, FG_F32);
-        auto zero = [&]() { if (M > 0) FG_CUDA(cudaMemsetAsync(t.data, 0, (size_t)M * E * sizeof(float), rt.stream)); };
+        // a part that can write its output instead of adding it needs no zeroed buffer
+        auto open = [&](bool can_overwrite) {
+            rt.overwrite = can_overwrite;
+            if (!can_overwrite && M > 0) FG_CUDA(cudaMemsetAsync(t.data, 0, (size_t)M * E * sizeof(float), rt.stream));
+        };
         // the norm that reads x after a sublayer: produced by the kernel that adds the sublayer's output
         auto join = [&](Norm *post, Norm *reader) -> Tensor {
             Tensor out;
@@ -716,13 +722,15 @@ public:
         };
         Norm *hand_over = (next_norm && next_norm->deferrable() && next_norm->weight() && E * sizeof(float) <= 48 * 1024) ? next_norm : nullptr;
         bool fuse_inner = E * sizeof(float) <= 48 * 1024;
-        zero();
+        open(mixer->can_overwrite());
         mixer->forward(rt, xn, nullptr, batch, io, t, nullptr);
+        rt.overwrite = false;
         if (!feed_forward) return finished(join(mixer_post_norm, hand_over), hand_over);
         Tensor hn = join(mixer_post_norm, fuse_inner ? feed_forward_norm : nullptr);
         if (!hn.defined()) hn = feed_forward_norm->forward(rt, x, nullptr, 0);
-        zero();
+        open(feed_forward->can_overwrite());
         feed_forward->forward(rt, hn, nullptr, batch, t, nullptr);
+        rt.overwrite = false;
         return finished(join(feed_forward_post_norm, hand_over), hand_over);
     }
 };

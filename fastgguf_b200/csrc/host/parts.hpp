@@ -29,6 +29,9 @@ struct Runtime {
     Arena *arena = nullptr;           // activations of the step being run
     bool recording = false;           // the step is being recorded into a CUDA graph
     bool plain_kernels = false;       // the safety switch: the any-size FMA kernels everywhere, bfloat16 included
+    // Set by a block around ONE call of a mixer or feed-forward whose can_overwrite() is true: the `residual` handed over
+    // holds nothing yet, and the part writes its output there instead of adding it (no zeroing pass in front).
+    bool overwrite = false;
 };
 
 struct TensorDecl {
@@ -126,6 +129,7 @@ public:
     virtual bool cache_request(CacheRequest *out) const { (void)out; return false; }
     virtual int64_t state_bytes() const { return 0; }
     virtual bool supports_deferred_norm() const { return false; }
+    virtual bool can_overwrite() const { return false; }      // honours Runtime::overwrite
     // adds its output into residual ([M, E] f32).  xn: normalised rows, or (deferred) a started norm;
     // emit_norm: start this norm from the updated residual and return it (only with supports_deferred_norm)
     virtual DeferredNorm forward(Runtime &rt, const Tensor &xn, const DeferredNorm *deferred, const Batch &batch,
@@ -137,6 +141,7 @@ public:
 class FeedForward : public Part {
 public:
     virtual bool supports_deferred_norm() const { return false; }
+    virtual bool can_overwrite() const { return false; }      // honours Runtime::overwrite
     virtual DeferredNorm forward(Runtime &rt, const Tensor &xn, const DeferredNorm *deferred, const Batch &batch,
                                  Tensor &residual, Norm *emit_norm) = 0;
 };

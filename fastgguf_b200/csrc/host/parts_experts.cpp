@@ -8,8 +8,10 @@
 //         and multiplies the expert's INPUT: out = sum_e expert_e(s_e x).  Expert: g = min(W_gate x, limit),
 //         u = clamp(W_up x, -limit, limit), y = g sigmoid(alpha g) (u + 1), output W_down y.  Because both first
 //         contractions are linear, s_e is applied to their float32 results.
-//         Rows are grouped by expert on the device (experts.cu); the host never learns the routing, so a recorded decode
-//         step replays with whatever the router chooses.
+//         Rows are grouped by expert on the device (experts.cu).  A decode step and short portions never tell the host
+//         the routing, so a recorded decode step replays with whatever the router chooses.  A long portion in bfloat16
+//         reads the experts' row counts back once (one small copy; such a step is never recorded) and runs each expert's
+//         two contractions over its run of rows on the tensor-core kernels every other projection uses.
 #include <cmath>
 
 #include "parts.hpp"
@@ -25,6 +27,7 @@ public:
         if (act != "relu2") fail(FG_E_CONFIG, "mlp: activation '" + act + "' is not known (known: relu2)");
     }
     std::vector<TensorDecl> tensor_decls() const override { return {{"up_proj.weight", {F_, E_}}, {"down_proj.weight", {E_, F_}}}; }
+    bool can_overwrite() const override { return true; }
     void load(const std::map<std::string, Weight> &tensors, Runtime &) override {
         up_ = Linear(tensor_of(tensors, "up_proj.weight"));
         down_ = Linear(tensor_of(tensors, "down_proj.weight"));
@@ -33,7 +36,7 @@ public:
         Tensor t = up_.forward(rt, xn, nullptr, Tensor(), rt.dtype, false, nullptr, nullptr);
         if (t.rows > 0) FG_LAUNCH("core", fg_activation, t.data, t.dtype, (long long)t.rows * t.ld, 0, rt.stream);
         DeferredNorm started;
-        down_.forward(rt, t, nullptr, residual, FG_F32, true, emit_norm, &started);
+        down_.forward(rt, t, nullptr, residual, FG_F32, !rt.overwrite, emit_norm, &started);
         return started;
     }
 
@@ -70,6 +73,7 @@ public:
         }
         return d;
     }
+    bool can_overwrite() const override { return true; }
     void load(const std::map<std::string, Weight> &tensors, Runtime &rt) override {
         router_ = Linear(tensor_of(tensors, "router.weight"));
         // experts one after another: [X, 2F, E] (gate rows, then up rows) and [X, E, F], in the engine's dtype
@@ -82,6 +86,14 @@ public:
         }
         w_in_ = concat_rows(in, rt.dtype, rt.stream);
         w_out_ = concat_rows(out, rt.dtype, rt.stream);
+        for (int e = 0; e < X_; e++) {
+            in_of_.push_back(Linear(w_in_).rows((int64_t)e * 2 * F_, (int64_t)(e + 1) * 2 * F_));
+            out_of_.push_back(Linear(w_out_).rows((int64_t)e * E_, (int64_t)(e + 1) * E_));
+        }
+        if (!counts_host_) FG_CUDA(cudaMallocHost((void **)&counts_host_, ((size_t)X_ + 1) * sizeof(int)));
+    }
+    ~MoEFeedForward() override {
+        if (counts_host_) cudaFreeHost(counts_host_);
     }
     DeferredNorm forward(Runtime &rt, const Tensor &xn, const DeferredNorm *, const Batch &, Tensor &residual, Norm *) override {
         const int M = (int)xn.rows, P = M * top_;
@@ -90,27 +102,54 @@ public:
         // plain contraction: float32 accumulation of the activations as they are, float32 logits
         Tensor z = rt.arena->matrix(M, X_, FG_F32);
         const Tensor &R = router_.weight().t;
-        FG_LAUNCH("core", fg_gemm_generic, xn.data, xn.dtype, (int)xn.ld, R.data, R.dtype, (int)R.ld, z.data, FG_F32, (int)z.ld, 0, M, X_, E_,
-                  rt.stream);
+        if (R.dtype == xn.dtype)
+            FG_LAUNCH("mix", fg_moe_logits, xn.data, (int)xn.ld, R.data, (int)R.ld, xn.dtype, z.ptr<float>(), M, X_, E_, rt.stream);
+        else
+            FG_LAUNCH("core", fg_gemm_generic, xn.data, xn.dtype, (int)xn.ld, R.data, R.dtype, (int)R.ld, z.data, FG_F32, (int)z.ld, 0, M, X_,
+                      E_, rt.stream);
         int *ints = (int *)rt.arena->alloc(((size_t)3 * P + X_ + 1) * sizeof(int));
         int *pair_expert = ints, *order = ints + P, *slot_of = ints + 2 * P, *offsets = ints + 3 * P;
         float *pair_weight = (float *)rt.arena->alloc((size_t)P * sizeof(float));
         FG_LAUNCH("mix", fg_moe_route, z.ptr<float>(), M, X_, top_, pair_expert, pair_weight, offsets, order, slot_of, rt.stream);
         Tensor y = rt.arena->matrix(P, F_, rt.dtype);
+        Tensor o = rt.arena->matrix(P, E_, FG_F32);
+        if (!rt.recording && !rt.plain_kernels && rt.dtype == FG_BF16 && P >= grouped_from_ && E_ % 8 == 0 && F_ % 8 == 0) {
+            // a long portion: the experts' row counts come to the host, and each expert's run of rows goes through the
+            // tensor-core contraction; gate and up leave it as float32, so the routing weight and the clamps see what
+            // the accumulators held
+            FG_CUDA(cudaMemcpyAsync(counts_host_, offsets, ((size_t)X_ + 1) * sizeof(int), cudaMemcpyDeviceToHost, rt.stream));
+            FG_CUDA(cudaStreamSynchronize(rt.stream));
+            Tensor xs = rt.arena->matrix(P, E_, rt.dtype);
+            FG_LAUNCH("mix", fg_moe_gather, xn.data, (int)xn.ld, xn.dtype, order, top_, xs.data, P, E_, rt.stream);
+            Tensor gu = rt.arena->matrix(P, (int64_t)2 * F_, FG_F32);
+            for (int e = 0; e < X_; e++) {
+                const int a = counts_host_[e], b = counts_host_[e + 1];
+                if (b > a) in_of_[(size_t)e].forward(rt, xs.row_range(a, b), nullptr, gu.row_range(a, b), FG_F32, false, nullptr, nullptr);
+            }
+            FG_LAUNCH("mix", fg_moe_act, gu.ptr<float>(), order, pair_weight, y.data, y.dtype, P, F_, limit_, alpha_, rt.stream);
+            for (int e = 0; e < X_; e++) {
+                const int a = counts_host_[e], b = counts_host_[e + 1];
+                if (b > a) out_of_[(size_t)e].forward(rt, y.row_range(a, b), nullptr, o.row_range(a, b), FG_F32, false, nullptr, nullptr);
+            }
+            FG_LAUNCH("mix", fg_moe_combine, o.ptr<float>(), (int)o.ld, slot_of, residual.ptr<float>(), M, top_, E_, rt.overwrite ? 0 : 1, rt.stream);
+            return DeferredNorm();
+        }
         FG_LAUNCH("mix", fg_moe_first, xn.data, (int)xn.ld, w_in_.t.data, y.data, (int)y.ld, rt.dtype, pair_expert, offsets, order, pair_weight,
                   M, X_, top_, F_, E_, limit_, alpha_, rt.stream);
-        Tensor o = rt.arena->matrix(P, E_, FG_F32);
         FG_LAUNCH("mix", fg_moe_second, y.data, (int)y.ld, w_out_.t.data, o.ptr<float>(), (int)o.ld, rt.dtype, pair_expert, offsets, order, M,
                   X_, top_, F_, E_, rt.stream);
-        FG_LAUNCH("mix", fg_moe_combine, o.ptr<float>(), (int)o.ld, slot_of, residual.ptr<float>(), M, top_, E_, 1, rt.stream);
+        FG_LAUNCH("mix", fg_moe_combine, o.ptr<float>(), (int)o.ld, slot_of, residual.ptr<float>(), M, top_, E_, rt.overwrite ? 0 : 1, rt.stream);
         return DeferredNorm();
     }
 
 private:
     int E_ = 0, F_ = 0, X_ = 0, top_ = 0;
     float limit_ = 0.f, alpha_ = 1.702f;
+    int grouped_from_ = 256;                 // pairs (rows x choices) from which a portion takes the contraction per expert
     Linear router_;
     Weight w_in_, w_out_;
+    std::vector<Linear> in_of_, out_of_;     // each expert's rows of w_in_ / w_out_
+    int *counts_host_ = nullptr;             // pinned: where the experts' runs of slots start
 };
 
 void add_expert_kinds(std::map<std::string, PartFactory> &ffs) {

@@ -54,6 +54,7 @@ public:
         return {{"q_proj.weight", {Q, E_}}, {"k_proj.weight", {Q, E_}}, {"v_proj.weight", {V, E_}}, {"g_proj.weight", {V, E_}},
                 {"o_proj.weight", {E_, V}}};
     }
+    bool can_overwrite() const override { return true; }
     int64_t state_bytes() const override { return (int64_t)H_ * dk_ * dv_ * (int64_t)sizeof(float); }
     void load(const std::map<std::string, Weight> &tensors, Runtime &rt) override {
         Weight q = tensor_of(tensors, "q_proj.weight"), k = tensor_of(tensors, "k_proj.weight");
@@ -114,7 +115,7 @@ public:
                       sin_t, decay_dev_.t.ptr<float>(), (float *)io.state, b.n_seq, H_, dk_, dv_, k_scale_, eps_, rt.stream);
         }
         DeferredNorm started;
-        o_.forward(rt, y, nullptr, residual, FG_F32, true, emit_norm, &started);
+        o_.forward(rt, y, nullptr, residual, FG_F32, !rt.overwrite, emit_norm, &started);
         return started;
     }
 

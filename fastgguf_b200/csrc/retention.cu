@@ -24,6 +24,15 @@
 #define RET_THREADS 256
 #define RC 32                       // tokens a chunk
 
+template <typename TO> __device__ __forceinline__ void store4(TO *dst, float a, float b, float c, float d);
+template <> __device__ __forceinline__ void store4<float>(float *dst, float a, float b, float c, float d) {
+    *(float4 *)dst = make_float4(a, b, c, d);
+}
+template <> __device__ __forceinline__ void store4<bf16>(bf16 *dst, float a, float b, float c, float d) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+    *(uint2 *)dst = make_uint2(*(uint32_t *)&lo, *(uint32_t *)&hi);
+}
+
 __device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
 
 // rotate pair (j, j + half) of head vector `src` at position pos into dst (shared memory), times `mul`
@@ -34,6 +43,33 @@ __device__ __forceinline__ void rotate_into(const float *__restrict__ src, float
         float a = src[j], b = src[j + half], c = cs[j], s = sn[j];
         dst[j] = (a * c - b * s) * mul;
         dst[j + half] = (b * c + a * s) * mul;
+    }
+}
+
+// The same for the n tokens of a chunk at once, all threads busy and many loads in flight: dst[t][..] (row stride
+// `stride`) = rotated head vector of token r0 + t, times mul (and, DECAY, times decay^(n - 1 - t)).
+template <bool DECAY>
+__device__ __forceinline__ void rotate_chunk_into(const float *__restrict__ proj, int ld, int r0, int n, size_t head_off, float *dst,
+                                                  int stride, int dk, const int *__restrict__ positions,
+                                                  const float *__restrict__ cos_t, const float *__restrict__ sin_t, float mul, float l2,
+                                                  int tid) {
+    const int half = dk >> 1;
+#pragma unroll 4
+    for (int e = tid; e < n * half; e += RET_THREADS) {
+        const int t = e / half, j = e - t * half;
+        const float *src = proj + (size_t)(r0 + t) * ld + head_off;
+        const int pos = positions[r0 + t];
+        const float a = src[j], b = src[j + half], c = cos_t[(size_t)pos * half + j], sn = sin_t[(size_t)pos * half + j];
+        const float m = DECAY ? mul * exp2f(l2 * (float)(n - 1 - t)) : mul;
+        dst[t * stride + j] = (a * c - b * sn) * m;
+        dst[t * stride + j + half] = (b * c + a * sn) * m;
+    }
+}
+__device__ __forceinline__ void copy_chunk_into(const float *__restrict__ proj, int ld, int r0, int n, size_t off, float *dst, int dv, int tid) {
+#pragma unroll 4
+    for (int e = tid; e < n * dv; e += RET_THREADS) {
+        const int t = e / dv, j = e - t * dv;
+        dst[e] = proj[(size_t)(r0 + t) * ld + off + j];
     }
 }
 
@@ -160,11 +196,23 @@ retention_chunk_scan_kernel(const int *__restrict__ seq_chunk0, const int *__res
     float *Sg = state + ((size_t)slots[seq] * H + h) * dk * dv + e;
     const float l2 = log2f(decay[h]);
     float s = *Sg;
-    for (int c = c0; c < c1; c++) {
-        float *u = U + ((size_t)c * H + h) * dk * dv + e;
-        float add = *u;
-        *u = s;
-        s = fmaf(s, exp2f(l2 * (float)chunk_len[c]), add);
+    const size_t step = (size_t)H * dk * dv;
+    float *u = U + ((size_t)c0 * H + h) * dk * dv + e;
+    for (int c = c0; c < c1; c += 8) {
+        // eight chunks' contributions are fetched before the first is used: the chain of sums does not wait for memory
+        float add[8], f[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            add[i] = c + i < c1 ? u[(size_t)i * step] : 0.f;
+            f[i] = c + i < c1 ? exp2f(l2 * (float)chunk_len[c + i]) : 1.f;
+        }
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            if (c + i >= c1) break;
+            u[(size_t)i * step] = s;
+            s = fmaf(s, f[i], add[i]);
+        }
+        u += 8 * step;
     }
     *Sg = s;
 }
@@ -246,6 +294,133 @@ retention_chunk_out_kernel(const float *__restrict__ proj, int ld, TO *__restric
     }
 }
 
+// ------------------------------------------------------------------ the chunked form with register tiles
+// The same three steps for head sizes 64 and 128 (keys and values each), where the tiles divide evenly: every thread
+// owns a small tile of the result and reads its operands sixteen bytes at a time, so that the FMA units, not the
+// load units, set the pace.  Sums run over the same terms in the same order as in the plain kernels above.
+
+// 1. U = K'^T V.  Thread (ti, tj): rows ti * TI .. + TI of U, columns tj * 4 .. + 4.
+template <int DK, int DV>
+__global__ void __launch_bounds__(RET_THREADS)
+retention_chunk_state_fast(const float *__restrict__ proj, int ld, const int *__restrict__ positions,
+                           const int *__restrict__ chunk_row, const int *__restrict__ chunk_len,
+                           const float *__restrict__ cos_t, const float *__restrict__ sin_t, const float *__restrict__ decay,
+                           float *__restrict__ U, int H, float k_scale) {
+    constexpr int NJ = DV / 4, NI = RET_THREADS / NJ, TI = DK / NI;
+    __shared__ __align__(16) float K[RC * DK];
+    __shared__ __align__(16) float V[RC * DV];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int c = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+    const int r0 = chunk_row[c], n = chunk_len[c];
+    const float l2 = log2f(decay[h]);
+    rotate_chunk_into<true>(proj, ld, r0, n, (size_t)(H + h) * DK, K, DK, DK, positions, cos_t, sin_t, k_scale, l2, tid);
+    copy_chunk_into(proj, ld, r0, n, (size_t)2 * H * DK + (size_t)h * DV, V, DV, tid);
+    __syncthreads();
+    const int tj = tid % NJ, ti = tid / NJ;
+    float acc[TI][4];
+#pragma unroll
+    for (int u = 0; u < TI; u++) acc[u][0] = acc[u][1] = acc[u][2] = acc[u][3] = 0.f;
+    for (int t = 0; t < n; t++) {
+        const float4 v = *(const float4 *)(V + t * DV + tj * 4);
+        float k[TI];
+#pragma unroll
+        for (int u = 0; u < TI; u += 4) *(float4 *)(k + u) = *(const float4 *)(K + t * DK + ti * TI + u);
+#pragma unroll
+        for (int u = 0; u < TI; u++) {
+            acc[u][0] = fmaf(k[u], v.x, acc[u][0]); acc[u][1] = fmaf(k[u], v.y, acc[u][1]);
+            acc[u][2] = fmaf(k[u], v.z, acc[u][2]); acc[u][3] = fmaf(k[u], v.w, acc[u][3]);
+        }
+    }
+    float *Ug = U + ((size_t)c * H + h) * DK * DV;
+#pragma unroll
+    for (int u = 0; u < TI; u++) *(float4 *)(Ug + (size_t)(ti * TI + u) * DV + tj * 4) = make_float4(acc[u][0], acc[u][1], acc[u][2], acc[u][3]);
+}
+
+// 3. Outputs.  Thread (ti, tj): tokens ti, ti + NI, ..., columns tj * 4 .. + 4; a token's row lies in NJ neighbouring lanes.
+template <int DK, int DV, typename TO>
+__global__ void __launch_bounds__(RET_THREADS)
+retention_chunk_out_fast(const float *__restrict__ proj, int ld, TO *__restrict__ out, int ldo, const int *__restrict__ positions,
+                         const int *__restrict__ chunk_row, const int *__restrict__ chunk_len, const float *__restrict__ cos_t,
+                         const float *__restrict__ sin_t, const float *__restrict__ decay, const float *__restrict__ U, int H,
+                         float k_scale, float eps) {
+    constexpr int NJ = DV / 4, NI = RET_THREADS / NJ, TT = RC / NI, DKP = DK + 4;
+    extern __shared__ __align__(16) float sm[];
+    float *Q = sm, *K = Q + RC * DKP, *V = K + RC * DKP, *A = V + RC * DV;       // Q, K: [RC][DKP]; V: [RC][DV]; A: [RC][RC]
+    pdl_launch_dependents();
+    pdl_wait();
+    const int c = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+    const int r0 = chunk_row[c], n = chunk_len[c];
+    const float l2 = log2f(decay[h]);
+    rotate_chunk_into<false>(proj, ld, r0, n, (size_t)h * DK, Q, DKP, DK, positions, cos_t, sin_t, 1.0f, 0.f, tid);
+    rotate_chunk_into<false>(proj, ld, r0, n, (size_t)(H + h) * DK, K, DKP, DK, positions, cos_t, sin_t, k_scale, 0.f, tid);
+    copy_chunk_into(proj, ld, r0, n, (size_t)2 * H * DK + (size_t)h * DV, V, DV, tid);
+    for (int e = n * DKP + tid; e < RC * DKP; e += RET_THREADS) Q[e] = K[e] = 0.f;       // rows of a short last chunk
+    for (int e = n * DV + tid; e < RC * DV; e += RET_THREADS) V[e] = 0.f;
+    __syncthreads();
+    // scores: four (i, j) pairs a thread
+    for (int e = tid; e < RC * RC; e += RET_THREADS) {
+        const int i = e / RC, j = e % RC;
+        float a = 0.f;
+        if (j <= i && i < n) {
+#pragma unroll 8
+            for (int d = 0; d < DK; d += 4) {
+                const float4 q = *(const float4 *)(Q + i * DKP + d), k = *(const float4 *)(K + j * DKP + d);
+                a = fmaf(q.x, k.x, a); a = fmaf(q.y, k.y, a); a = fmaf(q.z, k.z, a); a = fmaf(q.w, k.w, a);
+            }
+            a *= exp2f(l2 * (float)(i - j));
+        }
+        A[e] = a;
+    }
+    __syncthreads();
+    const int tj = tid % NJ, ti = tid / NJ;
+    const float *S = U + ((size_t)c * H + h) * DK * DV + tj * 4;
+    float acc[TT][4];
+#pragma unroll
+    for (int u = 0; u < TT; u++) acc[u][0] = acc[u][1] = acc[u][2] = acc[u][3] = 0.f;
+    // what the state before the chunk gives: Q S, four rows of S at a time
+#pragma unroll 2
+    for (int d = 0; d < DK; d += 4) {
+        const float4 s0 = *(const float4 *)(S + (size_t)d * DV), s1 = *(const float4 *)(S + (size_t)(d + 1) * DV);
+        const float4 s2 = *(const float4 *)(S + (size_t)(d + 2) * DV), s3 = *(const float4 *)(S + (size_t)(d + 3) * DV);
+#pragma unroll
+        for (int u = 0; u < TT; u++) {
+            const float4 q = *(const float4 *)(Q + (ti + u * NI) * DKP + d);
+            acc[u][0] = fmaf(q.x, s0.x, acc[u][0]); acc[u][1] = fmaf(q.x, s0.y, acc[u][1]); acc[u][2] = fmaf(q.x, s0.z, acc[u][2]); acc[u][3] = fmaf(q.x, s0.w, acc[u][3]);
+            acc[u][0] = fmaf(q.y, s1.x, acc[u][0]); acc[u][1] = fmaf(q.y, s1.y, acc[u][1]); acc[u][2] = fmaf(q.y, s1.z, acc[u][2]); acc[u][3] = fmaf(q.y, s1.w, acc[u][3]);
+            acc[u][0] = fmaf(q.z, s2.x, acc[u][0]); acc[u][1] = fmaf(q.z, s2.y, acc[u][1]); acc[u][2] = fmaf(q.z, s2.z, acc[u][2]); acc[u][3] = fmaf(q.z, s2.w, acc[u][3]);
+            acc[u][0] = fmaf(q.w, s3.x, acc[u][0]); acc[u][1] = fmaf(q.w, s3.y, acc[u][1]); acc[u][2] = fmaf(q.w, s3.z, acc[u][2]); acc[u][3] = fmaf(q.w, s3.w, acc[u][3]);
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < TT; u++) {
+        const float f = exp2f(l2 * (float)(ti + u * NI + 1));
+        acc[u][0] *= f; acc[u][1] *= f; acc[u][2] *= f; acc[u][3] *= f;
+    }
+    // what the chunk's own tokens give: A V (A is zero beyond a token's own place)
+    for (int t = 0; t < n; t++) {
+        const float4 v = *(const float4 *)(V + t * DV + tj * 4);
+#pragma unroll
+        for (int u = 0; u < TT; u++) {
+            const float a = A[(ti + u * NI) * RC + t];
+            acc[u][0] = fmaf(a, v.x, acc[u][0]); acc[u][1] = fmaf(a, v.y, acc[u][1]); acc[u][2] = fmaf(a, v.z, acc[u][2]); acc[u][3] = fmaf(a, v.w, acc[u][3]);
+        }
+    }
+    // unit norm over the head's values (NJ neighbouring lanes hold a token's row), gate, store
+#pragma unroll
+    for (int u = 0; u < TT; u++) {
+        const int i = ti + u * NI;
+        float ss = acc[u][0] * acc[u][0] + acc[u][1] * acc[u][1] + acc[u][2] * acc[u][2] + acc[u][3] * acc[u][3];
+#pragma unroll
+        for (int o = NJ / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (i >= n) continue;
+        const float inv = 1.0f / sqrtf(ss / (float)DV + eps);
+        const float4 g = *(const float4 *)(proj + (size_t)(r0 + i) * ld + (size_t)2 * H * DK + (size_t)(H + h) * DV + tj * 4);
+        TO *o = out + (size_t)(r0 + i) * ldo + (size_t)h * DV + tj * 4;
+        store4<TO>(o, acc[u][0] * inv * silu_f(g.x), acc[u][1] * inv * silu_f(g.y), acc[u][2] * inv * silu_f(g.z), acc[u][3] * inv * silu_f(g.w));
+    }
+}
+
 // ------------------------------------------------------------------ launchers
 static FgPerDevice g_seq_setup[2], g_state_setup, g_out_setup[2];
 
@@ -303,15 +478,42 @@ extern "C" int fg_retention_chunked(const float *proj, int ld, void *out, int ou
         if (e != cudaSuccess) return (int)e;
     }
     int *chunk_row = plan, *chunk_len = plan + n_chunks, *seq_chunk0 = plan + 2 * n_chunks;
+    // head sizes 64 / 128 with 16-byte aligned rows: the kernels with register tiles
+    const bool fast = (dk == 64 || dk == 128) && (dv == 64 || dv == 128) && ld % 4 == 0 && (((uintptr_t)proj | (uintptr_t)U) & 15) == 0 &&
+                      ldo % 4 == 0 && ((uintptr_t)out & 15) == 0;
     int code = fg_launch(retention_chunk_plan_kernel, dim3(1), dim3(n_seq >= 256 ? 256 : 32), 0, stream, cu_rows, n_seq, chunk_row, chunk_len,
                          seq_chunk0);
     if (code) return code;
-    code = fg_launch(retention_chunk_state_kernel, dim3(n_chunks, H), dim3(RET_THREADS), s1, stream, proj, ld, positions, (const int *)chunk_row,
-                         (const int *)chunk_len, cos_t, sin_t, decay, U, H, dk, dv, k_scale);
+#define RET_STATE_FAST(DK, DV) fg_launch(retention_chunk_state_fast<DK, DV>, dim3(n_chunks, H), dim3(RET_THREADS), 0, stream, proj, ld, positions, \
+        (const int *)chunk_row, (const int *)chunk_len, cos_t, sin_t, decay, U, H, k_scale)
+    if (fast) code = dk == 64 ? (dv == 64 ? RET_STATE_FAST(64, 64) : RET_STATE_FAST(64, 128)) : (dv == 64 ? RET_STATE_FAST(128, 64) : RET_STATE_FAST(128, 128));
+    else code = fg_launch(retention_chunk_state_kernel, dim3(n_chunks, H), dim3(RET_THREADS), s1, stream, proj, ld, positions, (const int *)chunk_row,
+                          (const int *)chunk_len, cos_t, sin_t, decay, U, H, dk, dv, k_scale);
+#undef RET_STATE_FAST
     if (code) return code;
     code = fg_launch(retention_chunk_scan_kernel, dim3(n_seq, H, (dk * dv + RET_THREADS - 1) / RET_THREADS), dim3(RET_THREADS), 0, stream,
                      (const int *)seq_chunk0, (const int *)chunk_len, slots, decay, U, state, H, dk, dv);
     if (code) return code;
+    if (fast) {
+        const size_t sf = ((size_t)2 * RC * (dk + 4) + (size_t)RC * dv + RC * RC) * sizeof(float);
+#define RET_OUT_FAST(DK, DV, TO) do { \
+        static FgPerDevice setup; \
+        if (fg_needs_setup(setup)) { \
+            cudaError_t e = cudaFuncSetAttribute(retention_chunk_out_fast<DK, DV, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024); \
+            if (e != cudaSuccess) return (int)e; \
+        } \
+        return fg_launch(retention_chunk_out_fast<DK, DV, TO>, dim3(n_chunks, H), dim3(RET_THREADS), sf, stream, proj, ld, (TO *)out, ldo, positions, \
+                         (const int *)chunk_row, (const int *)chunk_len, cos_t, sin_t, decay, (const float *)U, H, k_scale, eps); } while (0)
+#define RET_OUT_FAST_T(TO) do { \
+        if (dk == 64 && dv == 64) RET_OUT_FAST(64, 64, TO); \
+        if (dk == 64 && dv == 128) RET_OUT_FAST(64, 128, TO); \
+        if (dk == 128 && dv == 64) RET_OUT_FAST(128, 64, TO); \
+        RET_OUT_FAST(128, 128, TO); } while (0)
+        if (wide) RET_OUT_FAST_T(float);
+        RET_OUT_FAST_T(bf16);
+#undef RET_OUT_FAST_T
+#undef RET_OUT_FAST
+    }
     if (wide)
         return fg_launch(retention_chunk_out_kernel<float>, dim3(n_chunks, H), dim3(RET_THREADS), s3, stream, proj, ld, (float *)out, ldo,
                          positions, (const int *)chunk_row, (const int *)chunk_len, cos_t, sin_t, decay, (const float *)U, H, dk, dv, k_scale, eps);

@@ -138,6 +138,8 @@ MIXERS = {
     "long attention, head 128, kept keys and a wide window": attention(6, 1, 128, 128, 0.09, size=100, keep_first=5),
     "long attention, head 64, window alone": attention(2, 1, 64, 64, 0.125, size=65),
     "long retention, head 128": retention(2, 128, 128, [0.999, 0.99], rot=(10000.0, 64)),
+    "long retention, keys 64 and values 128": retention(2, 64, 128, [0.9, 0.9995], rot=(1000.0, 64)),
+    "long retention, keys 128 and values 64": retention(3, 128, 64, [1.0, 0.97, 0.5]),
 }
 
 
