@@ -12,25 +12,31 @@
 // ------------------------------------------------------------------ embedding gather
 template <typename TW>
 __global__ void embed_gather_kernel(const TW *__restrict__ table, const int *__restrict__ tokens,
-                                    float *__restrict__ x, int E) {
+                                    float *__restrict__ x, int E, float scale) {
     pdl_launch_dependents();
     pdl_wait();
     int m = blockIdx.x;
     const TW *row = table + (size_t)tokens[m] * E;
     float *out = x + (size_t)m * E;
-    for (int i = threadIdx.x; i < E; i += blockDim.x) out[i] = to_f32<TW>(row[i]);
+    for (int i = threadIdx.x; i < E; i += blockDim.x) out[i] = to_f32<TW>(row[i]) * scale;
+}
+
+// x = table[token] * scale (embd_scale of the reference, fastgguf.c:4652; 1 for most models)
+extern "C" int fg_embed_gather_scaled(const void *table, int table_dtype, const int *tokens, float *x,
+                                      int M, int E, float scale, cudaStream_t stream) {
+    if (M <= 0) return 0;
+    int threads = E >= 1024 ? 256 : 128;
+    if (table_dtype == FG_F32)
+        return fg_launch(embed_gather_kernel<float>, dim3(M), dim3(threads), 0, stream, (const float *)table, tokens, x, E, scale);
+    else if (table_dtype == FG_BF16)
+        return fg_launch(embed_gather_kernel<bf16>, dim3(M), dim3(threads), 0, stream, (const bf16 *)table, tokens, x, E, scale);
+    else return FG_ERR_BAD_DTYPE;
+    return FG_LAUNCH_CHECK();
 }
 
 extern "C" int fg_embed_gather(const void *table, int table_dtype, const int *tokens, float *x,
                                int M, int E, cudaStream_t stream) {
-    if (M <= 0) return 0;
-    int threads = E >= 1024 ? 256 : 128;
-    if (table_dtype == FG_F32)
-        return fg_launch(embed_gather_kernel<float>, dim3(M), dim3(threads), 0, stream, (const float *)table, tokens, x, E);
-    else if (table_dtype == FG_BF16)
-        return fg_launch(embed_gather_kernel<bf16>, dim3(M), dim3(threads), 0, stream, (const bf16 *)table, tokens, x, E);
-    else return FG_ERR_BAD_DTYPE;
-    return FG_LAUNCH_CHECK();
+    return fg_embed_gather_scaled(table, table_dtype, tokens, x, M, E, 1.0f, stream);
 }
 
 // The same gather that also starts a deferred RMSNorm: xw = bf16(x * norm_w) and the row's sum of squares

@@ -216,6 +216,9 @@ moe_tile_kernel(const T *__restrict__ A, int lda, const T *__restrict__ W, void 
 }
 
 // ------------------------------------------------------------------ a few rows (decode): a warp per output, weights streamed once per pair
+// (Pairs of one expert read the same rows at about the same time, so the second reader finds them in L2.  A form with a
+// block per expert that kept several slots' inputs in shared memory and read each weight row once was measured slower in
+// the replayed decode step: fewer warps in flight, and every row's sums wait for its own loads.)
 template <typename T, bool FIRST>
 __global__ void __launch_bounds__(256)
 moe_rows_kernel(const T *__restrict__ A, int lda, const T *__restrict__ W, void *__restrict__ out, int ldo,
@@ -271,7 +274,7 @@ extern "C" int fg_moe_first(const void *x, int ldx, const void *w_in, void *y, i
     if (M <= 0) return 0;
     const int P = M * top;
     if (dtype != FG_F32 && dtype != FG_BF16) return FG_ERR_BAD_DTYPE;
-    if (P <= 16 && (size_t)E * 4 <= 48 * 1024) {
+    if (P <= 64 && (size_t)E * 4 <= 48 * 1024) {
         dim3 grid((F + 7) / 8 < 128 ? (F + 7) / 8 : 128, P);
         if (dtype == FG_F32)
             return fg_launch(moe_rows_kernel<float, true>, grid, dim3(256), (size_t)E * 4, stream, (const float *)x, ldx, (const float *)w_in,
@@ -294,7 +297,7 @@ extern "C" int fg_moe_second(const void *y, int ldy, const void *w_out, float *o
     if (M <= 0) return 0;
     const int P = M * top;
     if (dtype != FG_F32 && dtype != FG_BF16) return FG_ERR_BAD_DTYPE;
-    if (P <= 16 && (size_t)F * 4 <= 48 * 1024) {
+    if (P <= 64 && (size_t)F * 4 <= 48 * 1024) {
         dim3 grid((E + 7) / 8 < 128 ? (E + 7) / 8 : 128, P);
         if (dtype == FG_F32)
             return fg_launch(moe_rows_kernel<float, false>, grid, dim3(256), (size_t)F * 4, stream, (const float *)y, ldy, (const float *)w_out,

@@ -22,6 +22,8 @@ extern "C" {
 
 /* ---- libfg_core: row-wise kernels, plain contraction, any-size attention, sampling */
 int fg_embed_gather(const void *table, int table_dtype, const int *tokens, float *x, int M, int E, cudaStream_t stream);
+int fg_embed_gather_scaled(const void *table, int table_dtype, const int *tokens, float *x, int M, int E, float scale,
+                           cudaStream_t stream);
 int fg_embed_gather_norm(const void *table, int table_dtype, const int *tokens, float *x, const float *norm_w,
                          void *xw, float *ss, int M, int E, cudaStream_t stream);
 int fg_rmsnorm(const float *x, const float *w, const int *rows, void *out, int out_dtype, int R, int E, float eps,

@@ -762,8 +762,7 @@ public:
             started.x = x; started.weight = emit_norm->weight();
             return started;
         }
-        FG_LAUNCH("core", fg_embed_gather, w_.t.data, w_.t.dtype, batch.tokens, x.ptr<float>(), M, (int)E_, rt.stream);
-        if (scale_ != 1.0f) dev_scale_f32(x.ptr<float>(), (int64_t)M * E_, scale_, rt.stream);
+        FG_LAUNCH("core", fg_embed_gather_scaled, w_.t.data, w_.t.dtype, batch.tokens, x.ptr<float>(), M, (int)E_, scale_, rt.stream);
         return started;
     }
 
