@@ -219,9 +219,9 @@ def compare_zirivik(args):
                           "prefill_ms": round(pms, 3), "prefill_tokens_per_s": round(PREFILL_TOKENS / (pms * 1e-3), 1),
                           "decode_ms_per_step": round(dms, 4), "decode_tokens_per_s": round(B * 1000.0 / dms, 1),
                           "launches_per_decode_step": launches,
-                          "profile_prefill": [{"name": r["name"], "calls": r["calls"], "ms": round(r["ms"], 4)} for r in prof_prefill[:16]],
+                          "profile_prefill": [{"name": r["name"], "calls": r["calls"], "ms": round(r["ms"], 4)} for r in prof_prefill],
                           "profile_prompt_and_8_decode_steps": [{"name": r["name"], "calls": r["calls"], "ms": round(r["ms"], 4)}
-                                                               for r in prof_all[:24]]}
+                                                               for r in prof_all]}
             del engine
         row["config"] = {"width": width, "heads": heads, "kv_heads": kv, "head_dim": hd, "ff": ff, "vocab": vocab, "window": window,
                          "experts": "8 of ff %d, 2 a row" % eff, "retention": "%d heads of 128 x 128" % (width // 128)}

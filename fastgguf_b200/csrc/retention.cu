@@ -183,38 +183,44 @@ retention_chunk_state_kernel(const float *__restrict__ proj, int ld, const int *
 
 // 2. The scan over a sequence's chunks, element by element: U[c] <- state before chunk c; the state after the last chunk
 //    goes back to the sequence's state row.  grid (sequences, heads, slices of dk * dv).
+template <typename V>          // V = float4 where a head's state is a multiple of four floats (16-byte accesses), else float
 __global__ void __launch_bounds__(RET_THREADS)
 retention_chunk_scan_kernel(const int *__restrict__ seq_chunk0, const int *__restrict__ chunk_len, const int *__restrict__ slots,
                             const float *__restrict__ decay, float *__restrict__ U, float *__restrict__ state, int H, int dk, int dv) {
     pdl_launch_dependents();
     pdl_wait();
+    constexpr int W = sizeof(V) / sizeof(float);
     const int seq = blockIdx.x, h = blockIdx.y;
-    const int e = blockIdx.z * RET_THREADS + threadIdx.x;
+    const int e = (blockIdx.z * RET_THREADS + threadIdx.x) * W;
     if (e >= dk * dv) return;
     const int c0 = seq_chunk0[seq], c1 = seq_chunk0[seq + 1];
     if (c1 <= c0) return;
-    float *Sg = state + ((size_t)slots[seq] * H + h) * dk * dv + e;
+    V *Sg = (V *)(state + ((size_t)slots[seq] * H + h) * dk * dv + e);
     const float l2 = log2f(decay[h]);
-    float s = *Sg;
+    V sv = *Sg;
+    float *s = (float *)&sv;
     const size_t step = (size_t)H * dk * dv;
     float *u = U + ((size_t)c0 * H + h) * dk * dv + e;
     for (int c = c0; c < c1; c += 8) {
         // eight chunks' contributions are fetched before the first is used: the chain of sums does not wait for memory
-        float add[8], f[8];
+        V add[8];
+        float f[8];
 #pragma unroll
         for (int i = 0; i < 8; i++) {
-            add[i] = c + i < c1 ? u[(size_t)i * step] : 0.f;
+            if (c + i < c1) add[i] = *(const V *)(u + (size_t)i * step);
             f[i] = c + i < c1 ? exp2f(l2 * (float)chunk_len[c + i]) : 1.f;
         }
 #pragma unroll
         for (int i = 0; i < 8; i++) {
             if (c + i >= c1) break;
-            u[(size_t)i * step] = s;
-            s = fmaf(s, f[i], add[i]);
+            *(V *)(u + (size_t)i * step) = sv;
+            const float *a = (const float *)&add[i];
+#pragma unroll
+            for (int w = 0; w < W; w++) s[w] = fmaf(s[w], f[i], a[w]);
         }
         u += 8 * step;
     }
-    *Sg = s;
+    *Sg = sv;
 }
 
 // 3. Outputs of a chunk.  One block per (chunk, head): A[i][j] = decay^(i-j) (q_i . k_j) for j <= i, then
@@ -379,7 +385,7 @@ retention_chunk_out_fast(const float *__restrict__ proj, int ld, TO *__restrict_
 #pragma unroll
     for (int u = 0; u < TT; u++) acc[u][0] = acc[u][1] = acc[u][2] = acc[u][3] = 0.f;
     // what the state before the chunk gives: Q S, four rows of S at a time
-#pragma unroll 2
+#pragma unroll 4
     for (int d = 0; d < DK; d += 4) {
         const float4 s0 = *(const float4 *)(S + (size_t)d * DV), s1 = *(const float4 *)(S + (size_t)(d + 1) * DV);
         const float4 s2 = *(const float4 *)(S + (size_t)(d + 2) * DV), s3 = *(const float4 *)(S + (size_t)(d + 3) * DV);
@@ -491,8 +497,12 @@ extern "C" int fg_retention_chunked(const float *proj, int ld, void *out, int ou
                           (const int *)chunk_len, cos_t, sin_t, decay, U, H, dk, dv, k_scale);
 #undef RET_STATE_FAST
     if (code) return code;
-    code = fg_launch(retention_chunk_scan_kernel, dim3(n_seq, H, (dk * dv + RET_THREADS - 1) / RET_THREADS), dim3(RET_THREADS), 0, stream,
-                     (const int *)seq_chunk0, (const int *)chunk_len, slots, decay, U, state, H, dk, dv);
+    if ((dk * dv) % 4 == 0 && (((uintptr_t)U | (uintptr_t)state) & 15) == 0)
+        code = fg_launch(retention_chunk_scan_kernel<float4>, dim3(n_seq, H, (dk * dv / 4 + RET_THREADS - 1) / RET_THREADS), dim3(RET_THREADS), 0,
+                         stream, (const int *)seq_chunk0, (const int *)chunk_len, slots, decay, U, state, H, dk, dv);
+    else
+        code = fg_launch(retention_chunk_scan_kernel<float>, dim3(n_seq, H, (dk * dv + RET_THREADS - 1) / RET_THREADS), dim3(RET_THREADS), 0, stream,
+                         (const int *)seq_chunk0, (const int *)chunk_len, slots, decay, U, state, H, dk, dv);
     if (code) return code;
     if (fast) {
         const size_t sf = ((size_t)2 * RC * (dk + 4) + (size_t)RC * dv + RC * RC) * sizeof(float);

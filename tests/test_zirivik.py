@@ -382,3 +382,22 @@ def test_generation_in_bfloat16_runs_the_recorded_step(models):
                     for i, t in enumerate(c.tokens))
         assert close >= 0.9 * len(c.tokens)
     eng.cache.check()
+
+
+def test_command_line_generates(models):
+    """``python -m fastgguf_b200 generate`` on a Zirivik folder: the model class comes from config.json, the tokens are
+    those of Engine.generate."""
+    import json
+    import os
+    import subprocess
+    import sys
+    d, cfg, W = models[("a", 1.0)]
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    p = subprocess.run([sys.executable, "-m", "fastgguf_b200", "generate", d, "256", "--prompt", "5,17,3,200", "--prompt", "9",
+                        "--temp", "0", "--max-tokens", "6", "--ignore-eos", "--dtype", "float32", "--json"],
+                       cwd=root, capture_output=True, text=True)
+    assert p.returncode == 0, p.stderr
+    got = [r["tokens"] for r in json.loads(p.stdout)]
+    eng = engine_for(d, "float32", max_tokens=512, max_batch=2)
+    want = [c.tokens for c in eng.generate([[5, 17, 3, 200], [9]], temp=0, max_tokens=6, ignore_eos=True)]
+    assert got == want
