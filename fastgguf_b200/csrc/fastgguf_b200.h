@@ -84,7 +84,8 @@ int fg_moe_second(const void *y, int ldy, const void *w_out, float *out, int ldo
 int fg_moe_combine(const float *slot_out, int ld, const int *slot_of, float *t, int M, int top, int E, int accumulate,
                    cudaStream_t stream);
 
-/* ---- libfg_tc: bf16 contraction on tcgen05 / TMA / tensor memory */
+/* ---- libfg_tc: bf16 contraction on tcgen05 / TMA / tensor memory
+ * epi: 0 bf16 out, 1 f32 out, 2 f32 out += (residual add), 3 silu(gate) * up on interleaved rows, 4 bf16 out of max(x, 0)^2 */
 int fg_gemm_tc(const void *X, int ldx, const void *W, int ldw, void *out, int ldc, int epi, int M, int N, int K,
                int force_splits, const float *ss_in, int ss_tiles, int ss_size, float ss_eps, const float *norm_w,
                void *xw_out, float *ss_out, int *ss_tiles_out /* host */, cudaStream_t stream);

@@ -47,7 +47,7 @@
 #define WAIT_LIMIT_CYCLES 2000000000ll
 #define WAIT_SHORT_CYCLES 1000000ll
 
-enum { EPI_BF16 = 0, EPI_F32 = 1, EPI_ADD_F32 = 2, EPI_SILU_MUL = 3 };
+enum { EPI_BF16 = 0, EPI_F32 = 1, EPI_ADD_F32 = 2, EPI_SILU_MUL = 3, EPI_RELU2_BF16 = 4 /* launcher only: EPI_BF16 + act */ };
 
 __device__ int g_gemm_error = 0;      // 0, or (code << 8 | role) of the first wait that ran out
 // How long a wait may last, in SM cycles (about a second).  A variable, so that a test can make a wait run out within a
@@ -203,7 +203,10 @@ struct GemmArgs {
     int epi, stages;      // decode kernel: epilogue and ring depth are run-time values
     int test_skip_copy;   // tests only: the decode kernel's producer omits the activation copy of its first stage
     int splits;           // prefill kernel: > 1 = partial products of `kb_per_split` K-blocks each into out[split][M][ldc]
+    int act;              // bf16 epilogue only: 1 = store max(x, 0)^2 (the squared ReLU of a plain feed-forward)
 };
+
+__device__ __forceinline__ float relu2(float x) { return x > 0.f ? x * x : 0.f; }
 
 __device__ __forceinline__ float inv_rms(const GemmArgs &a, int m) {
     float s = 0.f;
@@ -256,6 +259,10 @@ __device__ __forceinline__ void epilogue_token_major(const GemmArgs &a, uint32_t
             if (!m_ok || n0 >= a.N) continue;
 #pragma unroll
             for (int j = 0; j < 16; j++) v[j] *= iv;
+            if (EPI == EPI_BF16 && a.act) {
+#pragma unroll
+                for (int j = 0; j < 16; j++) v[j] = relu2(v[j]);
+            }
             const size_t idx = (out_row0 + (size_t)m) * a.ldc + n0;       // (out_row0: the split's block of a partial product)
             const bool full = a.vec_ok && n0 + 16 <= a.N;
             if (EPI == EPI_BF16) {
@@ -736,7 +743,7 @@ gemm_tc_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
                     const int n = p0 + lane + 32 * i;
                     if (n >= a.N) continue;
                     const size_t idx = (size_t)m * a.ldc + n;
-                    if (epi == EPI_BF16) ((bf16 *)a.out)[idx] = __float2bfloat16_rn(v[i]);
+                    if (epi == EPI_BF16) ((bf16 *)a.out)[idx] = __float2bfloat16_rn(a.act ? relu2(v[i]) : v[i]);
                     else {
                         ((float *)a.out)[idx] = v[i];
                         if (emit) a.xw_out[(size_t)m * a.N + n] = __float2bfloat16_rn(v[i] * nw_pre[i]);
@@ -942,7 +949,7 @@ gemm_splitk_finish_kernel(GemmArgs a, const float *__restrict__ ws, int S) {
         if (n >= a.N) continue;
         const size_t idx = (size_t)m * a.ldc + n;
         float x = v[i] * iv;
-        if (EPI == EPI_BF16) { ((bf16 *)a.out)[idx] = __float2bfloat16_rn(x); continue; }
+        if (EPI == EPI_BF16) { ((bf16 *)a.out)[idx] = __float2bfloat16_rn(a.act ? relu2(x) : x); continue; }
         if (EPI == EPI_ADD_F32) x += res[i];
         ((float *)a.out)[idx] = x;
         if (EPI == EPI_ADD_F32 && a.norm_w) {
@@ -1330,6 +1337,9 @@ extern "C" int fg_gemm_tc_ws(const void *X, int ldx, const void *W, int ldw, voi
                              void *workspace, long long workspace_bytes, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || K % 8 || ldx % 8 || ldw % 8 || ((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return FG_ERR_BAD_SIZE;
+    // epilogue code 4: bfloat16 output of max(x, 0)^2 - the bf16 epilogue with its activation flag set
+    const int act = epi == EPI_RELU2_BF16 ? 1 : 0;
+    if (act) epi = EPI_BF16;
     if (epi == EPI_SILU_MUL && N % 128) return FG_ERR_BAD_SIZE;
     // Up to 128 rows the weights stream through the decode kernel, in blocks of 64 tokens whose CTAs run side by side
     // and share each weight tile through L2; beyond that the prefill kernel is faster (measured: 56.6 against 45.5 k tok/s
@@ -1350,7 +1360,7 @@ extern "C" int fg_gemm_tc_ws(const void *X, int ldx, const void *W, int ldw, voi
             const int esz = (epi == EPI_F32 || epi == EPI_ADD_F32) ? 4 : 2;
             const int vec = ((uintptr_t)out % 16 == 0) && ((size_t)ldc * esz % 16 == 0);
             if (ss_tiles_out) *ss_tiles_out = (N + 127) / 128;
-            GemmArgs fin{out, M, N, K, ldc, kbs, vec, ss_in, ss_tiles, ss_size, ss_eps, norm_w, (bf16 *)xw_out, ss_out, epi, 0, 0, S};
+            GemmArgs fin{out, M, N, K, ldc, kbs, vec, ss_in, ss_tiles, ss_size, ss_eps, norm_w, (bf16 *)xw_out, ss_out, epi, 0, 0, S, act};
             dim3 grid((N + 127) / 128, (M + 7) / 8);
             const float *ws = (const float *)workspace;
             // The second kernel starts in plain stream order, when the partial products are complete.  Launched as a
@@ -1412,7 +1422,7 @@ extern "C" int fg_gemm_tc_ws(const void *X, int ldx, const void *W, int ldw, voi
     int vec_ok = ((uintptr_t)out % 16 == 0) && ((size_t)ldc * esz % 16 == 0);
     if (ss_tiles_out) *ss_tiles_out = (int)grid.y * (bn < 0 && epi == EPI_ADD_F32 ? 2 : 1);
     GemmArgs a{out, M, N, K, ldc, kb_per_split, vec_ok, ss_in, ss_tiles, ss_size, ss_eps, norm_w, (bf16 *)xw_out, ss_out, epi, 0,
-               g_test_skip_copy};
+               g_test_skip_copy, 0, act};
     switch (epi) {
     case EPI_BF16: return dispatch<EPI_BF16>(swap, bn, tmP, tmQ, a, grid, stream);
     case EPI_F32: return dispatch<EPI_F32>(swap, bn, tmP, tmQ, a, grid, stream);

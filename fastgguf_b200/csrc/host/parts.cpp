@@ -180,6 +180,32 @@ Tensor Linear::forward(Runtime &rt, const Tensor &a_in, const DeferredNorm *defe
     return out;
 }
 
+Tensor Linear::forward_relu2(Runtime &rt, const Tensor &a) const {
+    const Tensor &W = w_.t;
+    const int64_t M = a.rows, K = a.cols, N = W.rows;
+    if (K != W.cols) fail(FG_E_INTERNAL, "contraction: the input does not fit the weight");
+    if (fast_ && !rt.plain_kernels && a.dtype == FG_BF16 && rt.dtype == FG_BF16) {
+        Tensor out = rt.arena->matrix(M, N, FG_BF16);
+        if (M == 0) return out;
+        const int EPI_RELU2_BF16 = 4;
+        int tiles_out = 0;
+        count_launch();
+        ProfileScope scope("fg_gemm_tc", profile_on() ? format("%lld x %lld, %lld rows, relu2", (long long)N, (long long)K, (long long)M).c_str() : nullptr);
+        const long long ws_bytes = FG_KERNEL("tc", fg_gemm_tc_workspace_bytes)((int)M, (int)N, (int)K, EPI_RELU2_BF16);
+        void *ws = ws_bytes > 0 ? rt.arena->alloc((size_t)ws_bytes) : nullptr;
+        int code = FG_KERNEL("tc", fg_gemm_tc_ws)(a.data, (int)a.ld, W.data, (int)W.ld, out.data, (int)out.ld, EPI_RELU2_BF16, (int)M, (int)N,
+                                                  (int)K, 0, nullptr, 0, 1, 0.f, nullptr, nullptr, nullptr, &tiles_out, ws, ws_bytes,
+                                                  rt.stream);
+        if (code != KERNEL_BAD_SIZE) {
+            check_kernel(code, "fg_gemm_tc (relu2)");
+            return out;
+        }
+    }
+    Tensor t = forward(rt, a, nullptr, Tensor(), rt.dtype, false, nullptr, nullptr);
+    if (t.rows > 0) FG_LAUNCH("core", fg_activation, t.data, t.dtype, (long long)t.rows * t.ld, 0, rt.stream);
+    return t;
+}
+
 bool Linear::forward_silu(Runtime &rt, const Tensor &a_in, const DeferredNorm *deferred, Tensor *out) const {
     const Tensor &W = w_.t;
     Tensor a = deferred ? deferred->xw : a_in;

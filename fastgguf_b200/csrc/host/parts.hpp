@@ -230,6 +230,9 @@ public:
     // next norm started from the updated out when the tensor-core kernel ran (undefined when the plain one did).
     Tensor forward(Runtime &rt, const Tensor &a, const DeferredNorm *deferred, Tensor out, int out_dtype, bool accumulate,
                    Norm *emit_norm, DeferredNorm *emitted) const;
+    // max(a W^T, 0)^2 in the activation dtype: in the tensor-core kernel's epilogue where that kernel runs, else the
+    // contraction and an elementwise pass
+    Tensor forward_relu2(Runtime &rt, const Tensor &a) const;
     // silu(a gate^T) * (a up^T) as bf16 [M, F] from rows interleaved in blocks of 64; false if refused
     bool forward_silu(Runtime &rt, const Tensor &a, const DeferredNorm *deferred, Tensor *out) const;
 

@@ -33,8 +33,7 @@ public:
         down_ = Linear(tensor_of(tensors, "down_proj.weight"));
     }
     DeferredNorm forward(Runtime &rt, const Tensor &xn, const DeferredNorm *, const Batch &, Tensor &residual, Norm *emit_norm) override {
-        Tensor t = up_.forward(rt, xn, nullptr, Tensor(), rt.dtype, false, nullptr, nullptr);
-        if (t.rows > 0) FG_LAUNCH("core", fg_activation, t.data, t.dtype, (long long)t.rows * t.ld, 0, rt.stream);
+        Tensor t = up_.forward_relu2(rt, xn);
         DeferredNorm started;
         down_.forward(rt, t, nullptr, residual, FG_F32, !rt.overwrite, emit_norm, &started);
         return started;

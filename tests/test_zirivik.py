@@ -68,8 +68,10 @@ def test_norm_with_offset():
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("E,F,M", [(48, 72, 5), (64, 128, 70)])
+@pytest.mark.parametrize("E,F,M", [(48, 72, 5), (64, 128, 70), (256, 320, 300), (2048, 128, 200)])
 def test_dense_feed_forward(dtype, E, F, M):
+    """A few rows, a tile of rows, many rows, and a long reduction over few outputs (which the tensor-core contraction
+    splits along k): the squared ReLU sits in a different epilogue each time."""
     from fastgguf_b200.parts import run_part
     g = torch.Generator().manual_seed(2)
     W = {"mlp.up": (torch.randn(F, E, generator=g) / E ** 0.5).to(torch.bfloat16),
