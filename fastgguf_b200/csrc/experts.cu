@@ -219,12 +219,14 @@ moe_tile_kernel(const T *__restrict__ A, int lda, const T *__restrict__ W, void 
 // (Pairs of one expert read the same rows at about the same time, so the second reader finds them in L2.  A form with a
 // block per expert that kept several slots' inputs in shared memory and read each weight row once was measured slower in
 // the replayed decode step: fewer warps in flight, and every row's sums wait for its own loads.)
+// output rows a warp takes together: gate and up double the loads of a row, so two there and four for down
+#define MR_ROWS_OF(FIRST) ((FIRST) ? 2 : 4)
 template <typename T, bool FIRST>
 __global__ void __launch_bounds__(256)
 moe_rows_kernel(const T *__restrict__ A, int lda, const T *__restrict__ W, void *__restrict__ out, int ldo,
                 const int *__restrict__ pair_expert, const int *__restrict__ order, const float *__restrict__ pair_weight, int top,
                 int N, int K, float limit, float alpha) {
-    extern __shared__ float xs[];                    // [K] the slot's input row
+    extern __shared__ __align__(16) float xs[];      // [K] the slot's input row
     pdl_launch_dependents();
     pdl_wait();
     const int slot = blockIdx.y, pair = order[slot], e = pair_expert[pair];
@@ -236,33 +238,59 @@ moe_rows_kernel(const T *__restrict__ A, int lda, const T *__restrict__ W, void 
     const float w = FIRST ? pair_weight[pair] : 1.0f;
     constexpr int VEC = 16 / (int)sizeof(T);         // elements a 16-byte load brings
     const bool vec = (K % VEC) == 0 && (((uintptr_t)W) & 15) == 0;
-    for (int n = blockIdx.x * 8 + warp; n < N; n += gridDim.x * 8) {
-        const T *g = We + (size_t)n * K, *u = We + (size_t)(N + n) * K;
-        float sg = 0.f, su = 0.f;
+    constexpr int MR_ROWS = MR_ROWS_OF(FIRST);
+    // a warp takes MR_ROWS neighbouring output rows at a time: their weight rows are fetched together, so that many
+    // 16-byte loads are in flight in every lane
+    for (int n0 = (blockIdx.x * 8 + warp) * MR_ROWS; n0 < N; n0 += gridDim.x * 8 * MR_ROWS) {
+        float sg[MR_ROWS], su[MR_ROWS];
+#pragma unroll
+        for (int r = 0; r < MR_ROWS; r++) sg[r] = su[r] = 0.f;
         if (vec) {
+#pragma unroll 2
             for (int k = lane * VEC; k < K; k += 32 * VEC) {
-                const uint4 gv = *(const uint4 *)(g + k);
-                const T *ge = (const T *)&gv;
+                uint4 gv[MR_ROWS], uv[MR_ROWS];
 #pragma unroll
-                for (int i = 0; i < VEC; i++) sg = fmaf(xs[k + i], to_f32<T>(ge[i]), sg);
-                if (FIRST) {
-                    const uint4 uv = *(const uint4 *)(u + k);
-                    const T *ue = (const T *)&uv;
+                for (int r = 0; r < MR_ROWS; r++) {
+                    const int n = min(n0 + r, N - 1);                  // rows past the end repeat the last one; never stored
+                    gv[r] = *(const uint4 *)(We + (size_t)n * K + k);
+                    if (FIRST) uv[r] = *(const uint4 *)(We + (size_t)(N + n) * K + k);
+                }
+                float x[VEC];
 #pragma unroll
-                    for (int i = 0; i < VEC; i++) su = fmaf(xs[k + i], to_f32<T>(ue[i]), su);
+                for (int i = 0; i < VEC; i += 4) *(float4 *)(x + i) = *(const float4 *)(xs + k + i);
+#pragma unroll
+                for (int r = 0; r < MR_ROWS; r++) {
+                    const T *ge = (const T *)&gv[r], *ue = (const T *)&uv[r];
+#pragma unroll
+                    for (int i = 0; i < VEC; i++) {
+                        sg[r] = fmaf(x[i], to_f32<T>(ge[i]), sg[r]);
+                        if (FIRST) su[r] = fmaf(x[i], to_f32<T>(ue[i]), su[r]);
+                    }
                 }
             }
         } else {
             for (int k = lane; k < K; k += 32) {
-                sg = fmaf(xs[k], to_f32<T>(g[k]), sg);
-                if (FIRST) su = fmaf(xs[k], to_f32<T>(u[k]), su);
+#pragma unroll
+                for (int r = 0; r < MR_ROWS; r++) {
+                    const int n = min(n0 + r, N - 1);
+                    sg[r] = fmaf(xs[k], to_f32<T>(We[(size_t)n * K + k]), sg[r]);
+                    if (FIRST) su[r] = fmaf(xs[k], to_f32<T>(We[(size_t)(N + n) * K + k]), su[r]);
+                }
             }
         }
-        sg = warp_sum(sg);
-        if (FIRST) su = warp_sum(su);
+#pragma unroll
+        for (int r = 0; r < MR_ROWS; r++) {
+            sg[r] = warp_sum(sg[r]);
+            if (FIRST) su[r] = warp_sum(su[r]);
+        }
         if (lane == 0) {
-            if (FIRST) ((T *)out)[(size_t)slot * ldo + n] = from_f32<T>(expert_act(w * sg, w * su, limit, alpha));
-            else ((float *)out)[(size_t)slot * ldo + n] = sg;
+#pragma unroll
+            for (int r = 0; r < MR_ROWS; r++) {
+                const int n = n0 + r;
+                if (n >= N) break;
+                if (FIRST) ((T *)out)[(size_t)slot * ldo + n] = from_f32<T>(expert_act(w * sg[r], w * su[r], limit, alpha));
+                else ((float *)out)[(size_t)slot * ldo + n] = sg[r];
+            }
         }
     }
 }
@@ -275,7 +303,7 @@ extern "C" int fg_moe_first(const void *x, int ldx, const void *w_in, void *y, i
     const int P = M * top;
     if (dtype != FG_F32 && dtype != FG_BF16) return FG_ERR_BAD_DTYPE;
     if (P <= 64 && (size_t)E * 4 <= 48 * 1024) {
-        dim3 grid((F + 7) / 8 < 128 ? (F + 7) / 8 : 128, P);
+        dim3 grid((F + 8 * MR_ROWS_OF(true) - 1) / (8 * MR_ROWS_OF(true)), P);
         if (dtype == FG_F32)
             return fg_launch(moe_rows_kernel<float, true>, grid, dim3(256), (size_t)E * 4, stream, (const float *)x, ldx, (const float *)w_in,
                              y, ldy, pair_expert, order, pair_weight, top, F, E, limit, alpha);
@@ -298,7 +326,7 @@ extern "C" int fg_moe_second(const void *y, int ldy, const void *w_out, float *o
     const int P = M * top;
     if (dtype != FG_F32 && dtype != FG_BF16) return FG_ERR_BAD_DTYPE;
     if (P <= 64 && (size_t)F * 4 <= 48 * 1024) {
-        dim3 grid((E + 7) / 8 < 128 ? (E + 7) / 8 : 128, P);
+        dim3 grid((E + 8 * MR_ROWS_OF(false) - 1) / (8 * MR_ROWS_OF(false)), P);
         if (dtype == FG_F32)
             return fg_launch(moe_rows_kernel<float, false>, grid, dim3(256), (size_t)F * 4, stream, (const float *)y, ldy, (const float *)w_out,
                              (void *)out, ldo, pair_expert, order, (const float *)nullptr, top, E, F, 0.f, 0.f);
