@@ -200,7 +200,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
                        const bf16 *__restrict__ q, int ldq, bf16 *__restrict__ out, int ldo,
                        const int *__restrict__ cu_rows, const int *__restrict__ seq_start,
                        const int *__restrict__ block_table, int table_width, int KV, int G, float scale_log2, int window,
-                       int test_skip_copy) {
+                       int keep_first, int test_skip_copy) {
     constexpr int CH = HD / 64;                        // 64-wide chunks of the head dimension
     constexpr int KEYS = PIPE ? 64 : (HD > 64 ? 64 : 128), NPG = KEYS / PAGE;      // keys and pages per iteration
     constexpr int NS = PIPE ? 2 : 1;                   // score tiles in tensor memory, P tiles in shared memory
@@ -246,7 +246,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
     const int tile_hi = start + q0 + tq - 1;
     const int tile_lo = (window > 0 && start + q0 - window + 1 > 0) ? start + q0 - window + 1 : 0;
     const int p_begin = tile_lo / PAGE, p_end = tile_hi / PAGE + 1;
-    const int n_iter = active ? (p_end - p_begin + NPG - 1) / NPG : 0;
+    // Kept first keys: a row sees keys below min(keep_first, its window's start) besides its window.  The first nk
+    // iterations walk the sequence's first pages for them (each row masks what its window shows anyway, so a page that
+    // both walks reach is counted once), the others the window's pages as before.
+    const int keep = window > 0 ? keep_first : 0;
+    const int tile_lo_max = (window > 0 && tile_hi - window + 1 > 0) ? tile_hi - window + 1 : 0;       // the last row's window start
+    const int nk = active ? ((min(keep, tile_lo_max) + PAGE - 1) / PAGE + NPG - 1) / NPG : 0;
+    const int n_iter = active ? nk + (p_end - p_begin + NPG - 1) / NPG : 0;
+    auto first_page_of = [&](int j) { return j < nk ? NPG * j : p_begin + NPG * (j - nk); };
     const int *bt = block_table + (size_t)b * table_width;
 
     // ---- Q tile -> shared memory, swizzled like a TMA tile (rows past the valid ones are zero)
@@ -283,7 +290,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
         int k_issued = 0, v_issued = 0;
         auto page_rows = [&](int j, int (&y)[NPG]) {
             for (int h = 0; h < NPG; h++)
-                y[h] = (bt[min(p_begin + NPG * j + h, p_end - 1)] * KV + kvh) * PAGE;   // a page past the end is masked anyway
+                y[h] = (bt[min(first_page_of(j) + h, p_end - 1)] * KV + kvh) * PAGE;   // a page past the end is masked anyway
         };
         auto load_k = [&](int j) {
             int y[NPG];
@@ -373,8 +380,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
         bool ok = true;
         int j_last = -1;
         for (int j = set; j < n_iter; j += step) {
-            const int key0 = (p_begin + NPG * j) * PAGE;
-            const bool masked = key0 + KEYS - 1 > hi || key0 < lo;
+            const int key0 = first_page_of(j) * PAGE;
+            // the keys this row sees in this iteration: its window, or (kept iterations) what lies in front of it
+            const int lo_j = (j < nk && valid) ? INT_MIN : lo;
+            const int hi_j = (j < nk && valid) ? min(hi, min(keep, lo) - 1) : hi;
+            const bool masked = key0 + KEYS - 1 > hi_j || key0 < lo_j;
             if (!mbar_wait(s_full + 8 * tile_of(j), use_parity(j))) { raise_error(4); ok = false; break; }
             tc_fence_after();
             const uint32_t srow = trow + tile_of(j) * KEYS, pj = ps + tile_of(j) * P_TILE;
@@ -390,7 +400,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
                 const float neg_base = -base;
                 auto chunk = [&](int c, const float (&v)[32]) {
                     uint32_t w[16];
-                    if (any_masked) softmax_chunk<true>(v, key0 + c * 32, masked ? lo : INT_MIN, masked ? hi : INT_MAX, scale_log2, neg_base, mx_raw, acc, w);
+                    if (any_masked) softmax_chunk<true>(v, key0 + c * 32, masked ? lo_j : INT_MIN, masked ? hi_j : INT_MAX, scale_log2, neg_base, mx_raw, acc, w);
                     else softmax_chunk<false>(v, 0, 0, 0, scale_log2, neg_base, mx_raw, acc, w);
                     // 32 keys = four 16-byte chunks of this row, in the 64-key chunk c / 2
 #pragma unroll
@@ -442,7 +452,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
                     for (int i = 0; i < 32; i++) {
                         int key = key0 + c * 32 + i;
                         float x = v[i];
-                        if (masked && (key < lo || key > hi)) x = -INFINITY;
+                        if (masked && (key < lo_j || key > hi_j)) x = -INFINITY;
                         mx_raw = fmaxf(mx_raw, x);
                     }
                 }
@@ -566,7 +576,7 @@ static int pool_map(CUtensorMap *map, const void *pool, long long rows, int hd) 
 template <int HD, bool PIPE, bool PP>
 static int launch_tc(const CUtensorMap &tmK, const CUtensorMap &tmV, const void *q, int ldq, void *out, int ldo,
                      const int *cu_rows, const int *seq_start, const int *block_table, int table_width, int n_seq,
-                     int max_new, int H, int KV, float scale, int window, cudaStream_t stream) {
+                     int max_new, int H, int KV, float scale, int window, int keep_first, cudaStream_t stream) {
     constexpr int KEYS = PIPE ? 64 : (HD > 64 ? 64 : 128);
     constexpr int smem = ROWS * HD * 2 + 2 * KEYS * HD * 2 + (PIPE ? 2 : 1) * ROWS * KEYS * 2 + 1024;
     // the attributes belong to the function on ONE device: set them once on every device that launches
@@ -582,17 +592,17 @@ static int launch_tc(const CUtensorMap &tmK, const CUtensorMap &tmV, const void 
     int G = H / KV, Gc = G < 16 ? G : 16, TQ = ROWS / Gc;
     dim3 grid(KV * ((G + Gc - 1) / Gc), (max_new + TQ - 1) / TQ, n_seq);
     return fg_launch(attn_prefill_tc_kernel<HD, PIPE, PP>, grid, dim3(ATT_THREADS(PP)), (size_t)smem, stream, tmK, tmV, (const bf16 *)q, ldq,
-                     (bf16 *)out, ldo, cu_rows, seq_start, block_table, table_width, KV, G, scale * LOG2E, window, g_test_skip_copy);
+                     (bf16 *)out, ldo, cu_rows, seq_start, block_table, table_width, KV, G, scale * LOG2E, window, keep_first, g_test_skip_copy);
 }
 
-// Arguments as fg_attention_prefill, plus the number of pages in the pools.  Takes HD 64 and 128.
-extern "C" int fg_attention_prefill_tc(const void *q, int ldq, void *out, int ldo, const int *cu_rows,
-                                       const int *seq_start, const int *block_table, int table_width,
-                                       const void *k_pool, const void *v_pool, int n_pages, int n_seq, int max_new,
-                                       int H, int KV, int hd, int page_size, float scale, int window,
-                                       cudaStream_t stream) {
+// Arguments as fg_attention_prefill_kept, plus the number of pages in the pools.  Takes HD 64 and 128.
+extern "C" int fg_attention_prefill_tc_kept(const void *q, int ldq, void *out, int ldo, const int *cu_rows,
+                                            const int *seq_start, const int *block_table, int table_width,
+                                            const void *k_pool, const void *v_pool, int n_pages, int n_seq, int max_new,
+                                            int H, int KV, int hd, int page_size, float scale, int window, int keep_first,
+                                            cudaStream_t stream) {
     if (n_seq <= 0 || max_new <= 0) return 0;
-    if (page_size != PAGE || H % KV || n_seq > 65535 || ldq % 8 || ldo % 8 || ((uintptr_t)q & 15) || ((uintptr_t)out & 15) ||
+    if (keep_first < 0 || page_size != PAGE || H % KV || n_seq > 65535 || ldq % 8 || ldo % 8 || ((uintptr_t)q & 15) || ((uintptr_t)out & 15) ||
         ((uintptr_t)k_pool & 15) || ((uintptr_t)v_pool & 15) || (hd != 64 && hd != 128))
         return FG_ERR_BAD_SIZE;
     CUtensorMap tmK, tmV;
@@ -612,10 +622,19 @@ extern "C" int fg_attention_prefill_tc(const void *q, int ldq, void *out, int ld
     const bool pipe = g_variant >= 0 ? ((g_variant >> (hd == 64 ? 0 : 1)) & 1) != 0 : true;
     const bool pp = hd == 64 && pipe && (g_variant >= 0 ? (g_variant & 4) != 0 : (long long)n_seq * max_new >= 3072);
 #define TC_RUN(HD, PIPE, PP) launch_tc<HD, PIPE, PP>(tmK, tmV, q, ldq, out, ldo, cu_rows, seq_start, block_table, table_width, \
-                                                     n_seq, max_new, H, KV, scale, window, stream)
+                                                     n_seq, max_new, H, KV, scale, window, keep_first, stream)
     if (hd == 64) return pipe ? (pp ? TC_RUN(64, true, true) : TC_RUN(64, true, false)) : TC_RUN(64, false, false);
     return pipe ? TC_RUN(128, true, false) : TC_RUN(128, false, false);
 #undef TC_RUN
+}
+
+extern "C" int fg_attention_prefill_tc(const void *q, int ldq, void *out, int ldo, const int *cu_rows,
+                                       const int *seq_start, const int *block_table, int table_width,
+                                       const void *k_pool, const void *v_pool, int n_pages, int n_seq, int max_new,
+                                       int H, int KV, int hd, int page_size, float scale, int window,
+                                       cudaStream_t stream) {
+    return fg_attention_prefill_tc_kept(q, ldq, out, ldo, cu_rows, seq_start, block_table, table_width, k_pool, v_pool, n_pages, n_seq,
+                                        max_new, H, KV, hd, page_size, scale, window, 0, stream);
 }
 
 // For the test of the bounded waits: wait_limit_cycles > 0 sets how long a wait may last (0 restores the default of

@@ -246,7 +246,7 @@ int decode_splits(int n_sm, int n_seq, int n_heads, int n_kv_heads, int table_wi
 }
 
 // The tensor-core attention kernels take bfloat16, head size 64 / 128 for keys and values alike and pages of 64; other
-// sizes go to the any-size kernel.  Kept first keys: the mma.sync kernels walk their pages in front of the window's.
+// sizes go to the any-size kernel.  Kept first keys: every kernel walks their pages in front of the window's.
 static bool fast_attention_ok(const Runtime &rt, const Tensor &q, const LayerIO &io, const AttentionShape &a) {
     return !rt.plain_kernels && q.dtype == FG_BF16 && io.cache_dtype == FG_BF16 && (a.head_dim == 64 || a.head_dim == 128) &&
            a.v_head_dim == a.head_dim && io.page_size == 64 && q.ld % 2 == 0 && ((uintptr_t)q.data % 4) == 0;
@@ -271,12 +271,11 @@ static Tensor attention(Runtime &rt, const Tensor &q, const Batch &b, const Laye
         }
         // Many new tokens: 128-row tiles on the tcgen05 tensor cores.  A few rows (a sequence fed in short
         // pieces) waste less of the mma.sync kernel's 64-row tile.
-        // The tcgen05 kernel knows a plain window only; with kept first keys every portion takes the mma.sync kernel.
-        bool tc = b.max_new * (H / KV) >= 64 && q.ld % 8 == 0 && ((uintptr_t)q.data % 16) == 0 && !(a.window > 0 && a.keep_first > 0);
+        bool tc = b.max_new * (H / KV) >= 64 && q.ld % 8 == 0 && ((uintptr_t)q.data % 16) == 0;
         if (tc)
-            FG_LAUNCH("attn", fg_attention_prefill_tc, q.data, (int)q.ld, out.data, (int)out.ld, b.cu_rows, b.seq_start, table,
+            FG_LAUNCH("attn", fg_attention_prefill_tc_kept, q.data, (int)q.ld, out.data, (int)out.ld, b.cu_rows, b.seq_start, table,
                       b.table_width, io.k_pool, io.v_pool, io.n_pages, b.n_seq, b.max_new, H, KV, hd, io.page_size, a.scale, a.window,
-                      rt.stream);
+                      a.keep_first, rt.stream);
         else
             FG_LAUNCH("attn", fg_attention_prefill_kept, q.data, (int)q.ld, out.data, (int)out.ld, b.cu_rows, b.seq_start, table,
                       b.table_width, io.k_pool, io.v_pool, b.n_seq, b.max_new, H, KV, hd, io.page_size, a.scale, a.window, a.keep_first,

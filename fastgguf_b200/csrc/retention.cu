@@ -133,12 +133,10 @@ __global__ void retention_chunk_plan_kernel(const int *__restrict__ cu_rows, int
                                             int *__restrict__ chunk_len, int *__restrict__ seq_chunk0) {
     pdl_launch_dependents();
     pdl_wait();
-    __shared__ int total;
     if (threadIdx.x == 0) {
         int at = 0;
         for (int s = 0; s < n_seq; s++) { seq_chunk0[s] = at; at += (cu_rows[s + 1] - cu_rows[s] + RC - 1) / RC; }
         seq_chunk0[n_seq] = at;
-        total = at;
     }
     __syncthreads();
     for (int s = threadIdx.x; s < n_seq; s += blockDim.x) {
