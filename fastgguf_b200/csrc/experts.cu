@@ -216,9 +216,8 @@ moe_tile_kernel(const T *__restrict__ A, int lda, const T *__restrict__ W, void 
 }
 
 // ------------------------------------------------------------------ a few rows (decode): a warp per output, weights streamed once per pair
-// (Pairs of one expert read the same rows at about the same time, so the second reader finds them in L2.  A form with a
-// block per expert that kept several slots' inputs in shared memory and read each weight row once was measured slower in
-// the replayed decode step: fewer warps in flight, and every row's sums wait for its own loads.)
+// (Pairs of one expert read the same rows at about the same time, so the second reader finds them in L2.  The kernel
+// further down reads an expert's rows once for all its slots; this one takes what that one refuses.)
 // output rows a warp takes together: gate and up double the loads of a row, so two there and four for down
 #define MR_ROWS_OF(FIRST) ((FIRST) ? 2 : 4)
 template <typename T, bool FIRST>
@@ -295,6 +294,124 @@ moe_rows_kernel(const T *__restrict__ A, int lda, const T *__restrict__ W, void 
     }
 }
 
+// ------------------------------------------------------------------ a few rows (decode), an expert's weights read once
+// grid (blocks of output rows, experts).  A block of expert e takes the expert's slots up to four at a time: their input
+// rows wait in shared memory as float32, and every warp reads its MR_ROWS weight rows once, in runs of 16 bytes, for
+// all of them - where the kernel above reads them once per slot and leaves it to L2 to see the repeats.  Experts no row
+// chose leave at once.  Sums run along k in the same order as above, so a slot's result does not depend on its company.
+#define MG_SLOTS 4
+// FASTGGUF_MOE_GROUPED=0: the kernel above instead (for measurements)
+static bool moe_grouped_enabled() {
+    static int v = -1;
+    if (v < 0) { const char *e = getenv("FASTGGUF_MOE_GROUPED"); v = !(e && e[0] == '0'); }
+    return v != 0;
+}
+template <typename T, bool FIRST, int CNT>
+__device__ __forceinline__ void moe_group_rows(const T *__restrict__ We, const float *xs, void *__restrict__ out, int ldo, int s0,
+                                               const float (&w)[MG_SLOTS], int N, int K, float limit, float alpha, int n0, int lane) {
+    constexpr int R = MR_ROWS_OF(FIRST), VEC = 16 / (int)sizeof(T);
+    float sg[CNT][R], su[CNT][R];
+#pragma unroll
+    for (int i = 0; i < CNT; i++)
+#pragma unroll
+        for (int r = 0; r < R; r++) sg[i][r] = su[i][r] = 0.f;
+#pragma unroll 2
+    for (int k = lane * VEC; k < K; k += 32 * VEC) {
+        uint4 gv[R], uv[R];
+#pragma unroll
+        for (int r = 0; r < R; r++) {
+            const int n = min(n0 + r, N - 1);
+            gv[r] = *(const uint4 *)(We + (size_t)n * K + k);
+            if (FIRST) uv[r] = *(const uint4 *)(We + (size_t)(N + n) * K + k);
+        }
+#pragma unroll
+        for (int i = 0; i < CNT; i++) {
+            float x[VEC];
+#pragma unroll
+            for (int j = 0; j < VEC; j += 4) *(float4 *)(x + j) = *(const float4 *)(xs + i * K + k + j);
+#pragma unroll
+            for (int r = 0; r < R; r++) {
+                const T *ge = (const T *)&gv[r], *ue = (const T *)&uv[r];
+#pragma unroll
+                for (int j = 0; j < VEC; j++) {
+                    sg[i][r] = fmaf(x[j], to_f32<T>(ge[j]), sg[i][r]);
+                    if (FIRST) su[i][r] = fmaf(x[j], to_f32<T>(ue[j]), su[i][r]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < CNT; i++)
+#pragma unroll
+        for (int r = 0; r < R; r++) {
+            sg[i][r] = warp_sum(sg[i][r]);
+            if (FIRST) su[i][r] = warp_sum(su[i][r]);
+        }
+    if (lane == 0) {
+#pragma unroll
+        for (int i = 0; i < CNT; i++)
+#pragma unroll
+            for (int r = 0; r < R; r++) {
+                const int n = n0 + r;
+                if (n >= N) break;
+                if (FIRST) ((T *)out)[(size_t)(s0 + i) * ldo + n] = from_f32<T>(expert_act(w[i] * sg[i][r], w[i] * su[i][r], limit, alpha));
+                else ((float *)out)[(size_t)(s0 + i) * ldo + n] = sg[i][r];
+            }
+    }
+}
+
+template <typename T, bool FIRST>
+__global__ void __launch_bounds__(256)
+moe_rows_grouped_kernel(const T *__restrict__ A, int lda, const T *__restrict__ W, void *__restrict__ out, int ldo,
+                        const int *__restrict__ offsets, const int *__restrict__ order, const float *__restrict__ pair_weight, int top,
+                        int N, int K, float limit, float alpha) {
+    extern __shared__ __align__(16) float xs[];      // [MG_SLOTS][K]
+    pdl_launch_dependents();
+    pdl_wait();
+    const int e = blockIdx.y, s_begin = offsets[e], s_end = offsets[e + 1];
+    if (s_end <= s_begin) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const T *We = W + (size_t)e * (FIRST ? 2 : 1) * N * K;
+    const int n0 = (blockIdx.x * 8 + warp) * MR_ROWS_OF(FIRST);
+    for (int s0 = s_begin; s0 < s_end; s0 += MG_SLOTS) {
+        const int cnt = min(MG_SLOTS, s_end - s0);
+        __syncthreads();                             // the rows of the group before are no longer read
+        for (int i = 0; i < cnt; i++) {
+            const T *a = A + (size_t)(FIRST ? order[s0 + i] / top : s0 + i) * lda;
+            for (int k = threadIdx.x; k < K; k += 256) xs[i * K + k] = to_f32<T>(a[k]);
+        }
+        __syncthreads();
+        float w[MG_SLOTS];
+#pragma unroll
+        for (int i = 0; i < MG_SLOTS; i++) w[i] = (FIRST && i < cnt) ? pair_weight[order[s0 + i]] : 1.0f;
+        if (n0 >= N) continue;
+        switch (cnt) {
+        case 1: moe_group_rows<T, FIRST, 1>(We, xs, out, ldo, s0, w, N, K, limit, alpha, n0, lane); break;
+        case 2: moe_group_rows<T, FIRST, 2>(We, xs, out, ldo, s0, w, N, K, limit, alpha, n0, lane); break;
+        case 3: moe_group_rows<T, FIRST, 3>(We, xs, out, ldo, s0, w, N, K, limit, alpha, n0, lane); break;
+        default: moe_group_rows<T, FIRST, 4>(We, xs, out, ldo, s0, w, N, K, limit, alpha, n0, lane); break;
+        }
+    }
+}
+
+// takes sizes whose rows allow 16-byte loads and whose four input rows fit shared memory
+static bool moe_grouped_ok(int dtype, int K, const void *W) {
+    const int per = dtype == FG_F32 ? 4 : 8;
+    return K % per == 0 && (((uintptr_t)W) & 15) == 0 && (size_t)MG_SLOTS * K * sizeof(float) <= 96 * 1024;
+}
+template <typename T, bool FIRST>
+static int moe_grouped_launch(const void *A, int lda, const void *W, void *out, int ldo, const int *offsets, const int *order,
+                              const float *pair_weight, int X, int top, int N, int K, float limit, float alpha, cudaStream_t stream) {
+    static FgPerDevice setup;
+    if (fg_needs_setup(setup)) {
+        cudaError_t e = cudaFuncSetAttribute(moe_rows_grouped_kernel<T, FIRST>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+        if (e != cudaSuccess) return (int)e;
+    }
+    const int per_block = 8 * MR_ROWS_OF(FIRST);
+    return fg_launch(moe_rows_grouped_kernel<T, FIRST>, dim3((N + per_block - 1) / per_block, X), dim3(256), (size_t)MG_SLOTS * K * sizeof(float),
+                     stream, (const T *)A, lda, (const T *)W, out, ldo, offsets, order, pair_weight, top, N, K, limit, alpha);
+}
+
 // y: [M * top, F] in T.  x: [M, E].  w_in: [X, 2F, E].
 extern "C" int fg_moe_first(const void *x, int ldx, const void *w_in, void *y, int ldy, int dtype, const int *pair_expert,
                             const int *offsets, const int *order, const float *pair_weight, int M, int X, int top, int F, int E,
@@ -302,6 +419,10 @@ extern "C" int fg_moe_first(const void *x, int ldx, const void *w_in, void *y, i
     if (M <= 0) return 0;
     const int P = M * top;
     if (dtype != FG_F32 && dtype != FG_BF16) return FG_ERR_BAD_DTYPE;
+    if (P <= 64 && moe_grouped_ok(dtype, E, w_in) && moe_grouped_enabled()) {
+        if (dtype == FG_F32) return moe_grouped_launch<float, true>(x, ldx, w_in, y, ldy, offsets, order, pair_weight, X, top, F, E, limit, alpha, stream);
+        return moe_grouped_launch<bf16, true>(x, ldx, w_in, y, ldy, offsets, order, pair_weight, X, top, F, E, limit, alpha, stream);
+    }
     if (P <= 64 && (size_t)E * 4 <= 48 * 1024) {
         dim3 grid((F + 8 * MR_ROWS_OF(true) - 1) / (8 * MR_ROWS_OF(true)), P);
         if (dtype == FG_F32)
@@ -325,6 +446,10 @@ extern "C" int fg_moe_second(const void *y, int ldy, const void *w_out, float *o
     if (M <= 0) return 0;
     const int P = M * top;
     if (dtype != FG_F32 && dtype != FG_BF16) return FG_ERR_BAD_DTYPE;
+    if (P <= 64 && moe_grouped_ok(dtype, F, w_out) && moe_grouped_enabled()) {
+        if (dtype == FG_F32) return moe_grouped_launch<float, false>(y, ldy, w_out, out, ldo, offsets, order, nullptr, X, top, E, F, 0.f, 0.f, stream);
+        return moe_grouped_launch<bf16, false>(y, ldy, w_out, out, ldo, offsets, order, nullptr, X, top, E, F, 0.f, 0.f, stream);
+    }
     if (P <= 64 && (size_t)F * 4 <= 48 * 1024) {
         dim3 grid((E + 8 * MR_ROWS_OF(false) - 1) / (8 * MR_ROWS_OF(false)), P);
         if (dtype == FG_F32)
