@@ -17,8 +17,9 @@ from zirivik_cases import CASES, attention, config, dense, make_model, moe, rete
 
 pytestmark = pytest.mark.gpu
 
-#: max |dlogit| / max |logit| against the float64 plain implementation; about twice the worst any test here shows
-TOL = {"float32": 5e-6, "bfloat16": 6e-2}
+#: max |dlogit| / max |logit| against the float64 plain implementation; about twice the worst any test shows (float32
+#: 5.9e-6 among the random configurations, bfloat16 3.7e-2); a key wrongly seen or a lost state is at 1e-3 and above
+TOL = {"float32": 1.5e-5, "bfloat16": 6e-2}
 
 
 def tokens_for(cfg, n, seed):
