@@ -97,6 +97,10 @@ int fg_gemm_tc_ws(const void *X, int ldx, const void *W, int ldw, void *out, int
                   cudaStream_t stream);
 long long fg_gemm_tc_workspace_bytes(int M, int N, int K, int epi);
 int fg_gemm_tc_max_ss_tiles(int N);
+/* grouped contraction over runs of rows, each with its own matrix of a stack (see gemm_tc.cu); tiles: device int4 table */
+int fg_gemm_tc_grouped_bn(int N);
+int fg_gemm_tc_grouped(const void *X, int ldx, int rows, const void *W, int ldw, int stack_rows, float *out, int ldc, int N, int K,
+                       const void *tiles, int n_tiles, cudaStream_t stream);
 int fg_gemm_tc_error(void);
 /* tests only: shorten the bounded waits and make the decode kernel's pipeline stall, see gemm_tc.cu */
 int fg_gemm_tc_test_hook(long long wait_limit_cycles, int skip_copy);

@@ -204,6 +204,9 @@ struct GemmArgs {
     int test_skip_copy;   // tests only: the decode kernel's producer omits the activation copy of its first stage
     int splits;           // prefill kernel: > 1 = partial products of `kb_per_split` K-blocks each into out[split][M][ldc]
     int act;              // bf16 epilogue only: 1 = store max(x, 0)^2 (the squared ReLU of a plain feed-forward)
+    // prefill kernel, grouped contraction (rows in runs, each run with a weight matrix of its own out of a stack): tile t
+    // is tiles[t] = {first row, end of its run, first row of the run's matrix in W, tile index along N}; null: one matrix
+    const int4 *tiles;
 };
 
 __device__ __forceinline__ float relu2(float x) { return x > 0.f ? x * x : 0.f; }
@@ -818,7 +821,9 @@ gemm_tc_prefill_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_con
         int s = 0, ph = 0, issued = 0;                 // ring position, pass over the ring (parity), stages filled so far
         bool ok = true;
         for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-            const int t2 = tile % per_split, p0 = (t2 % n_pt) * BM, q0 = (t2 / n_pt) * BN;
+            const int t2 = tile % per_split;
+            int p0 = (t2 % n_pt) * BM, q0 = (t2 / n_pt) * BN;
+            if (a.tiles) { const int4 tt = a.tiles[tile]; p0 = tt.x; q0 = tt.z + tt.w * BN; }      // q0: the row in the stack of matrices
             int kb_begin, kb_end;
             kb_range(tile, kb_begin, kb_end);
             for (int kb = kb_begin; kb < kb_end; kb++) {
@@ -882,7 +887,13 @@ gemm_tc_prefill_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_con
             if (!mbar_wait(tfull0 + 8 * acc, (i >> 1) & 1)) { raise_error(3); break; }
             tc_fence_after();
             const uint32_t trow = tmem_base + ((uint32_t)(lg * 32) << 16) + acc * BN;
-            if (EPI == EPI_ADD_F32 && a.vec_ok && (a.N & 31) == 0)
+            if (a.tiles) {
+                // a run's tile: rows past the run's end belong to the next run (another matrix) and are not stored
+                const int4 tt = a.tiles[tile];
+                GemmArgs run = a;
+                run.M = tt.y;
+                epilogue_token_major<BN, EPI>(run, trow, tt.x, tt.w * BN, tt.w, prow, 0);
+            } else if (EPI == EPI_ADD_F32 && a.vec_ok && (a.N & 31) == 0)
                 epilogue_add_coalesced<BN>(a, trow, pt * BM, qt * BN, qt, lg, lane, smem + STAGES * STAGE_BYTES + lg * EPI_STAGE_BYTES);
             else
                 epilogue_token_major<BN, EPI>(a, trow, pt * BM, qt * BN, qt, prow, (size_t)(tile / per_split) * (size_t)a.M);
@@ -1192,7 +1203,7 @@ static int launch_decode(const CUtensorMap &tmW, const CUtensorMap &tmX, GemmArg
 }
 
 template <int BN, int STAGES, int EPI>
-static int launch_prefill(const CUtensorMap &tmP, const CUtensorMap &tmQ, const GemmArgs &a, cudaStream_t stream) {
+static int launch_prefill(const CUtensorMap &tmP, const CUtensorMap &tmQ, const GemmArgs &a, cudaStream_t stream, int table_tiles = 0) {
     constexpr int smem = STAGES * (BM + BN) * BK * 2 + 1024 + (EPI == EPI_ADD_F32 ? 4 * EPI_STAGE_BYTES : 0);
     static FgPerDevice configured;
     static int n_sm = 0;
@@ -1204,6 +1215,7 @@ static int launch_prefill(const CUtensorMap &tmP, const CUtensorMap &tmQ, const 
         if (cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sm <= 0) n_sm = 148;
     }
     int n_pt = (a.M + BM - 1) / BM, n_tiles = n_pt * ((a.N + BN - 1) / BN) * (a.splits > 1 ? a.splits : 1);
+    if (a.tiles) n_tiles = table_tiles;                // a grouped contraction: as many tiles as its table has
     dim3 grid(n_tiles < n_sm ? n_tiles : n_sm);
     return fg_launch(gemm_tc_prefill_kernel<BN, STAGES, EPI>, grid, dim3(GEMM_THREADS), (size_t)smem, stream, tmP, tmQ, a,
                      n_pt, n_tiles);
@@ -1430,6 +1442,32 @@ extern "C" int fg_gemm_tc_ws(const void *X, int ldx, const void *W, int ldw, voi
     case EPI_SILU_MUL: return dispatch<EPI_SILU_MUL>(swap, bn, tmP, tmQ, a, grid, stream);
     }
     return FG_ERR_BAD_DTYPE;
+}
+
+// Grouped contraction (the experts of a mixture over rows sorted by expert): rows [tiles[t].x, tiles[t].y) of X times the
+// matrix that starts at row tiles[t].z of the stack W ([stack_rows, K], every matrix N rows), columns tiles[t].w * BN ..
+// of the run's output, float32 out[rows, ldc].  One launch over all runs on the persistent prefill kernel: a tile of the
+// table is a tile of the kernel, the rest (ring, accumulators in tensor memory, epilogue under the next tile's MMAs) is
+// the plain contraction's.  fg_gemm_tc_grouped_bn(N) is the tile width the table must be built for; a tile's rows past
+// its run's end are computed and not stored.
+extern "C" int fg_gemm_tc_grouped_bn(int N) { return N % 256 == 0 ? 256 : 128; }
+
+extern "C" int fg_gemm_tc_grouped(const void *X, int ldx, int rows, const void *W, int ldw, int stack_rows, float *out, int ldc,
+                                  int N, int K, const void *tiles, int n_tiles, cudaStream_t stream) {
+    if (rows <= 0 || n_tiles <= 0) return 0;
+    if (N <= 0 || K <= 0 || K % 8 || ldx % 8 || ldw % 8 || ((uintptr_t)X & 15) || ((uintptr_t)W & 15) || ((uintptr_t)tiles & 15))
+        return FG_ERR_BAD_SIZE;
+    const int bn = fg_gemm_tc_grouped_bn(N);
+    CUtensorMap tmP, tmQ;
+    int e = make_map(&tmP, X, rows, K, ldx, BM);
+    if (e) return e;
+    e = make_map(&tmQ, W, stack_rows, K, ldw, bn);
+    if (e) return e;
+    const int vec_ok = ((uintptr_t)out % 16 == 0) && ((size_t)ldc * 4 % 16 == 0);
+    GemmArgs a{out, rows, N, K, ldc, 0, vec_ok, nullptr, 0, 1, 0.f, nullptr, nullptr, nullptr, EPI_F32, 0, g_test_skip_copy, 0, 0,
+               (const int4 *)tiles};
+    if (bn == 256) return launch_prefill<256, 4, EPI_F32>(tmP, tmQ, a, stream, n_tiles);
+    return launch_prefill<128, 6, EPI_F32>(tmP, tmQ, a, stream, n_tiles);
 }
 
 // For the test of the bounded waits: wait_limit_cycles > 0 sets how long a wait may last (0 restores the default of

@@ -10,8 +10,10 @@
 //         contractions are linear, s_e is applied to their float32 results.
 //         Rows are grouped by expert on the device (experts.cu).  A decode step and short portions never tell the host
 //         the routing, so a recorded decode step replays with whatever the router chooses.  A long portion in bfloat16
-//         reads the experts' row counts back once (one small copy; such a step is never recorded) and runs each expert's
-//         two contractions over its run of rows on the tensor-core kernels every other projection uses.
+//         reads the experts' row counts back once (one small copy; such a step is never recorded) and runs the experts'
+//         contractions over their runs of rows as ONE grouped launch each of the tensor-core kernel every other
+//         projection uses (a table of tiles tells it which rows meet which expert's matrix).
+#include <algorithm>
 #include <cmath>
 
 #include "parts.hpp"
@@ -85,14 +87,11 @@ public:
         }
         w_in_ = concat_rows(in, rt.dtype, rt.stream);
         w_out_ = concat_rows(out, rt.dtype, rt.stream);
-        for (int e = 0; e < X_; e++) {
-            in_of_.push_back(Linear(w_in_).rows((int64_t)e * 2 * F_, (int64_t)(e + 1) * 2 * F_));
-            out_of_.push_back(Linear(w_out_).rows((int64_t)e * E_, (int64_t)(e + 1) * E_));
-        }
         if (!counts_host_) FG_CUDA(cudaMallocHost((void **)&counts_host_, ((size_t)X_ + 1) * sizeof(int)));
     }
     ~MoEFeedForward() override {
         if (counts_host_) cudaFreeHost(counts_host_);
+        if (tiles_host_) cudaFreeHost(tiles_host_);
     }
     DeferredNorm forward(Runtime &rt, const Tensor &xn, const DeferredNorm *, const Batch &, Tensor &residual, Norm *) override {
         const int M = (int)xn.rows, P = M * top_;
@@ -113,7 +112,7 @@ public:
         Tensor y = rt.arena->matrix(P, F_, rt.dtype);
         Tensor o = rt.arena->matrix(P, E_, FG_F32);
         if (!rt.recording && !rt.plain_kernels && rt.dtype == FG_BF16 && P >= grouped_from_ && E_ % 8 == 0 && F_ % 8 == 0) {
-            // a long portion: the experts' row counts come to the host, and each expert's run of rows goes through the
+            // a long portion: the experts' row counts come to the host, and the experts' runs of rows go through the
             // tensor-core contraction; gate and up leave it as float32, so the routing weight and the clamps see what
             // the accumulators held
             FG_CUDA(cudaMemcpyAsync(counts_host_, offsets, ((size_t)X_ + 1) * sizeof(int), cudaMemcpyDeviceToHost, rt.stream));
@@ -121,15 +120,39 @@ public:
             Tensor xs = rt.arena->matrix(P, E_, rt.dtype);
             FG_LAUNCH("mix", fg_moe_gather, xn.data, (int)xn.ld, xn.dtype, order, top_, xs.data, P, E_, rt.stream);
             Tensor gu = rt.arena->matrix(P, (int64_t)2 * F_, FG_F32);
-            for (int e = 0; e < X_; e++) {
-                const int a = counts_host_[e], b = counts_host_[e + 1];
-                if (b > a) in_of_[(size_t)e].forward(rt, xs.row_range(a, b), nullptr, gu.row_range(a, b), FG_F32, false, nullptr, nullptr);
+            // both contractions as ONE launch each over all experts: a table of tiles {first row, end of the expert's run,
+            // the expert's first row in the stack, tile along the outputs}, an expert's tiles side by side so that its
+            // weights stay in L2 while its row tiles pass
+            const int bn1 = FG_KERNEL("tc", fg_gemm_tc_grouped_bn)(2 * F_), bn2 = FG_KERNEL("tc", fg_gemm_tc_grouped_bn)(E_);
+            auto count_tiles = [&](int N, int bn) {
+                size_t n = 0;
+                for (int e = 0; e < X_; e++) n += (size_t)((counts_host_[e + 1] - counts_host_[e] + 127) / 128) * (size_t)((N + bn - 1) / bn);
+                return n;
+            };
+            const size_t n1 = count_tiles(2 * F_, bn1), n2 = count_tiles(E_, bn2);
+            if (tiles_cap_ < n1 + n2) {
+                if (tiles_host_) FG_CUDA(cudaFreeHost(tiles_host_));
+                tiles_host_ = nullptr;
+                tiles_cap_ = std::max<size_t>(2 * (n1 + n2), 1024);
+                FG_CUDA(cudaMallocHost((void **)&tiles_host_, tiles_cap_ * 4 * sizeof(int)));
             }
+            auto fill = [&](int *t, int N, int bn) {
+                for (int e = 0; e < X_; e++) {
+                    const int a = counts_host_[e], b = counts_host_[e + 1];
+                    for (int qt = 0; qt < (N + bn - 1) / bn; qt++)
+                        for (int r = a; r < b; r += 128) { *t++ = r; *t++ = b; *t++ = e * N; *t++ = qt; }
+                }
+            };
+            fill(tiles_host_, 2 * F_, bn1);
+            fill(tiles_host_ + 4 * n1, E_, bn2);
+            int *tiles_dev = (int *)rt.arena->alloc((n1 + n2) * 4 * sizeof(int));
+            // (the stream was waited for above, after this buffer's last copy was queued: it is free to be rewritten)
+            FG_CUDA(cudaMemcpyAsync(tiles_dev, tiles_host_, (n1 + n2) * 4 * sizeof(int), cudaMemcpyHostToDevice, rt.stream));
+            FG_LAUNCH("tc", fg_gemm_tc_grouped, xs.data, (int)xs.ld, P, w_in_.t.data, (int)w_in_.t.ld, (int)w_in_.t.rows, gu.ptr<float>(),
+                      (int)gu.ld, 2 * F_, E_, tiles_dev, (int)n1, rt.stream);
             FG_LAUNCH("mix", fg_moe_act, gu.ptr<float>(), order, pair_weight, y.data, y.dtype, P, F_, limit_, alpha_, rt.stream);
-            for (int e = 0; e < X_; e++) {
-                const int a = counts_host_[e], b = counts_host_[e + 1];
-                if (b > a) out_of_[(size_t)e].forward(rt, y.row_range(a, b), nullptr, o.row_range(a, b), FG_F32, false, nullptr, nullptr);
-            }
+            FG_LAUNCH("tc", fg_gemm_tc_grouped, y.data, (int)y.ld, P, w_out_.t.data, (int)w_out_.t.ld, (int)w_out_.t.rows, o.ptr<float>(),
+                      (int)o.ld, E_, F_, tiles_dev + 4 * n1, (int)n2, rt.stream);
             FG_LAUNCH("mix", fg_moe_combine, o.ptr<float>(), (int)o.ld, slot_of, residual.ptr<float>(), M, top_, E_, rt.overwrite ? 0 : 1, rt.stream);
             return DeferredNorm();
         }
@@ -147,8 +170,9 @@ private:
     int grouped_from_ = 256;                 // pairs (rows x choices) from which a portion takes the contraction per expert
     Linear router_;
     Weight w_in_, w_out_;
-    std::vector<Linear> in_of_, out_of_;     // each expert's rows of w_in_ / w_out_
     int *counts_host_ = nullptr;             // pinned: where the experts' runs of slots start
+    int *tiles_host_ = nullptr;              // pinned: the tile tables of a long portion's two contractions
+    size_t tiles_cap_ = 0;
 };
 
 void add_expert_kinds(std::map<std::string, PartFactory> &ffs) {
