@@ -2,5 +2,6 @@
 from .base import ConfigError, ModelConfig, architecture_name, read_config_json
 from .llama import LlamaConfig
 from .zirivik import ZirivikConfig
+from .salulorn import SalulornConfig
 
-__all__ = ["ConfigError", "ModelConfig", "LlamaConfig", "ZirivikConfig", "architecture_name", "read_config_json"]
+__all__ = ["ConfigError", "ModelConfig", "LlamaConfig", "ZirivikConfig", "SalulornConfig", "architecture_name", "read_config_json"]

@@ -7,6 +7,13 @@
 // h / (H / KV) (:4781).  A window of w keeps only the last w positions (:4754-4758).
 // keep_first > 0 adds the sequence's first keep_first positions to what a windowed row sees (they keep
 // their places; a row sees each key once).  Values may have another size (hdv) than keys (hd).
+// softcap c > 0: a score becomes c * tanh(score / c) after the scale.  sinks: one float per query head whose
+// exponential joins the softmax's denominator - a key without a value; it is neither scaled nor capped.  The running
+// maximum and sum simply start at (sink, 1) instead of (-inf, 0).
+// latent != 0: the cache holds one small latent per position in v_pool (hdv numbers, which serve as the value as
+// well) and a rotated key part in k_pool (hd numbers); a query row then has hdv + hd numbers a head, and a score is
+// q[0:hdv] . latent + q[hdv:] . rotated part.  This is attention over keys and values that are linear maps of the
+// latent, with the key map folded into the query and the value map applied to the output by the caller.
 //
 // Keys are visited in chunks of CHUNK visible keys, the kept first ones and then the window from lo, with a running maximum and
 // sum in f32 (online softmax).  Within a chunk a thread scores whole keys; for the weighted sum of
@@ -18,7 +25,7 @@
 
 #define ATT_THREADS 256
 #define ATT_WARPS (ATT_THREADS / 32)
-#define MAX_DPL 8                     // output dimensions a lane owns at most: head sizes up to 256
+#define MAX_DPL 16                    // output dimensions a lane owns at most: value sizes up to 512
 #define CHUNK 1024
 
 template <typename T, int DPL>          // DPL: output dimensions a lane owns (32 * DPL >= head size)
@@ -27,10 +34,12 @@ attention_generic_kernel(const T *__restrict__ q, int ldq, T *__restrict__ out, 
                          const int *__restrict__ positions, const int *__restrict__ row_seq,
                          const int *__restrict__ block_table, int table_width,
                          const T *__restrict__ k_pool, const T *__restrict__ v_pool,
-                         int H, int KV, int hd, int hdv, int page_size, float scale, int window, int keep_first) {
+                         int H, int KV, int hd, int hdv, int page_size, float scale, int window, int keep_first,
+                         float softcap, const float *__restrict__ sinks, int latent) {
     extern __shared__ float smem[];
-    float *qs = smem;                 // [hd]
-    float *sc = smem + hd;            // [CHUNK]
+    const int qd = latent ? hdv + hd : hd;      // numbers a query head holds
+    float *qs = smem;                 // [qd]
+    float *sc = smem + qd;            // [CHUNK]
     __shared__ float scratch[32];
     int m = blockIdx.x, h = blockIdx.y;
     int kvh = h / (H / KV);
@@ -39,13 +48,14 @@ attention_generic_kernel(const T *__restrict__ q, int ldq, T *__restrict__ out, 
     const int n_first = min(keep_first, lo);          // kept first keys that lie in front of the window
     const int n_keys = n_first + pos - lo + 1;        // visible key v is position v (v < n_first) or lo + v - n_first
     const int *bt = block_table + (size_t)row_seq[m] * table_width;
-    const T *qrow = q + (size_t)m * ldq + (size_t)h * hd;
-    for (int d = threadIdx.x; d < hd; d += ATT_THREADS) qs[d] = to_f32<T>(qrow[d]);
+    const T *qrow = q + (size_t)m * ldq + (size_t)h * qd;
+    for (int d = threadIdx.x; d < qd; d += ATT_THREADS) qs[d] = to_f32<T>(qrow[d]);
+    const float *qk = latent ? qs + hdv : qs;   // the part of the query that meets k_pool
     __syncthreads();
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     float *part = sc + CHUNK;         // [ATT_WARPS][hdv] partial value sums of a chunk
-    float m_run = -INFINITY, l_run = 0.f;
+    float m_run = sinks ? sinks[h] : -INFINITY, l_run = sinks ? 1.f : 0.f;
     float acc[DPL];               // warp 0 keeps the running output: dims lane + 32 j
 #pragma unroll
     for (int j = 0; j < DPL; j++) acc[j] = 0.f;
@@ -60,15 +70,20 @@ attention_generic_kernel(const T *__restrict__ q, int ldq, T *__restrict__ out, 
                 // 16-byte loads along the key's row (rows of a pool start 16-byte aligned when hd is a multiple of 4)
                 for (int d = 0; d < hd; d += 4) {
                     const float4 kv4 = *(const float4 *)((const float *)kr + d);
-                    s = fmaf(qs[d], kv4.x, s);
-                    s = fmaf(qs[d + 1], kv4.y, s);
-                    s = fmaf(qs[d + 2], kv4.z, s);
-                    s = fmaf(qs[d + 3], kv4.w, s);
+                    s = fmaf(qk[d], kv4.x, s);
+                    s = fmaf(qk[d + 1], kv4.y, s);
+                    s = fmaf(qk[d + 2], kv4.z, s);
+                    s = fmaf(qk[d + 3], kv4.w, s);
                 }
             } else {
-                for (int d = 0; d < hd; d++) s = fmaf(qs[d], to_f32<T>(kr[d]), s);
+                for (int d = 0; d < hd; d++) s = fmaf(qk[d], to_f32<T>(kr[d]), s);
+            }
+            if (latent) {
+                const T *lr = v_pool + (((size_t)bt[p / page_size] * KV + kvh) * page_size + p % page_size) * hdv;
+                for (int d = 0; d < hdv; d++) s = fmaf(qs[d], to_f32<T>(lr[d]), s);
             }
             s *= scale;
+            if (softcap > 0.f) s = softcap * tanhf(s / softcap);
             sc[i] = s;
             cmax = fmaxf(cmax, s);
         }
@@ -81,7 +96,7 @@ attention_generic_kernel(const T *__restrict__ q, int ldq, T *__restrict__ out, 
             csum += e;
         }
         csum = block_sum(csum, scratch);   // its barriers also publish sc[] to every thread
-        float corr = expf(m_run - m_new);  // 0 on the first chunk (m_run = -inf)
+        float corr = expf(m_run - m_new);  // 0 on the first chunk without a sink (m_run = -inf)
         l_run = l_run * corr + csum;
         // values: warp w takes keys [w * run, (w + 1) * run) of the chunk, page by page, eight rows in flight
         const int run = (n + ATT_WARPS - 1) / ATT_WARPS;
@@ -140,26 +155,37 @@ attention_generic_kernel(const T *__restrict__ q, int ldq, T *__restrict__ out, 
     }
 }
 
-extern "C" int fg_attention_generic_kept(const void *q, int ldq, void *out, int ldo, int dtype,
-                                         const int *positions, const int *row_seq, const int *block_table,
-                                         int table_width, const void *k_pool, const void *v_pool,
-                                         int M, int H, int KV, int hd, int hdv, int page_size, float scale, int window,
-                                         int keep_first, cudaStream_t stream) {
+extern "C" int fg_attention_generic_ext(const void *q, int ldq, void *out, int ldo, int dtype,
+                                        const int *positions, const int *row_seq, const int *block_table,
+                                        int table_width, const void *k_pool, const void *v_pool,
+                                        int M, int H, int KV, int hd, int hdv, int page_size, float scale, int window,
+                                        int keep_first, float softcap, const float *sinks, int latent, cudaStream_t stream) {
     if (M <= 0) return 0;
-    const int big = hd > hdv ? hd : hdv;
-    if (big > 32 * MAX_DPL || hd <= 0 || hdv <= 0 || H % KV != 0 || H > 65535 || keep_first < 0) return FG_ERR_BAD_SIZE;
+    if (hdv > 32 * MAX_DPL || hd <= 0 || hdv <= 0 || H % KV != 0 || H > 65535 || keep_first < 0 || softcap < 0.f) return FG_ERR_BAD_SIZE;
     dim3 grid(M, H);
-    size_t smem = (size_t)(hd + CHUNK + ATT_WARPS * hdv) * sizeof(float);
+    size_t smem = (size_t)((latent ? hd + hdv : hd) + CHUNK + ATT_WARPS * hdv) * sizeof(float);
+    if (smem > 48 * 1024) return FG_ERR_BAD_SIZE;
 #define ATT_LAUNCH(T, DPL) attention_generic_kernel<T, DPL><<<grid, ATT_THREADS, smem, stream>>>((const T *)q, ldq, (T *)out, ldo, \
         positions, row_seq, block_table, table_width, (const T *)k_pool, (const T *)v_pool, H, KV, hd, hdv, page_size, scale, window, \
-        window > 0 ? keep_first : 0)
-#define ATT_BY_SIZE(T) do { if (hdv <= 64) ATT_LAUNCH(T, 2); else if (hdv <= 128) ATT_LAUNCH(T, 4); else ATT_LAUNCH(T, 8); } while (0)
+        window > 0 ? keep_first : 0, softcap, sinks, latent)
+#define ATT_BY_SIZE(T) do { if (hdv <= 64) ATT_LAUNCH(T, 2); else if (hdv <= 128) ATT_LAUNCH(T, 4); else if (hdv <= 256) ATT_LAUNCH(T, 8); \
+                            else ATT_LAUNCH(T, 16); } while (0)
     if (dtype == FG_F32) ATT_BY_SIZE(float);
     else if (dtype == FG_BF16) ATT_BY_SIZE(bf16);
     else return FG_ERR_BAD_DTYPE;
 #undef ATT_BY_SIZE
 #undef ATT_LAUNCH
     return FG_LAUNCH_CHECK();
+}
+
+extern "C" int fg_attention_generic_kept(const void *q, int ldq, void *out, int ldo, int dtype,
+                                         const int *positions, const int *row_seq, const int *block_table,
+                                         int table_width, const void *k_pool, const void *v_pool,
+                                         int M, int H, int KV, int hd, int hdv, int page_size, float scale, int window,
+                                         int keep_first, cudaStream_t stream) {
+    if (hd > 256 || hdv > 256) return FG_ERR_BAD_SIZE;
+    return fg_attention_generic_ext(q, ldq, out, ldo, dtype, positions, row_seq, block_table, table_width, k_pool, v_pool, M, H, KV,
+                                    hd, hdv, page_size, scale, window, keep_first, 0.f, nullptr, 0, stream);
 }
 
 extern "C" int fg_attention_generic(const void *q, int ldq, void *out, int ldo, int dtype,

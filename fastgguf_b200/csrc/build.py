@@ -31,12 +31,13 @@ MODULES = {
     "core": ["elementwise.cu", "gemm_generic.cu", "attention_generic.cu", "sampling.cu"],
     "tc": ["gemm_tc.cu"],
     "attn": ["attention_decode.cu", "attention_prefill.cu", "attention_prefill_tc.cu"],
-    # retention (linear attention with a state per sequence) and the mixture of experts
-    "mix": ["retention.cu", "experts.cu"],
+    # mixers beyond plain attention: retention and gated linear attention (a state per sequence), what stands between an
+    # attention mixer's projections and its scores (convolution, norms, adjacent-pair rotation, latents), and the experts
+    "mix": ["retention.cu", "experts.cu", "gla.cu", "attention_prep.cu"],
     # the C++ host: configuration, weights, cache, step function, generation loop, C interface; it opens the
     # kernel libraries above by name when a model first needs them
-    "engine": ["host/api.cpp", "host/cache.cpp", "host/config.cpp", "host/config_zirivik.cpp", "host/device.cpp", "host/model.cpp", "host/parts.cpp",
-               "host/parts_recurrent.cpp", "host/parts_experts.cpp", "host/runner.cpp", "host/safetensors.cpp", "host/host_kernels.cu"],
+    "engine": ["host/api.cpp", "host/cache.cpp", "host/config.cpp", "host/config_zirivik.cpp", "host/config_salulorn.cpp", "host/device.cpp", "host/model.cpp", "host/parts.cpp",
+               "host/parts_recurrent.cpp", "host/parts_attention.cpp", "host/parts_experts.cpp", "host/runner.cpp", "host/safetensors.cpp", "host/host_kernels.cu"],
 }
 LINK_FLAGS = {"engine": ["-ldl"]}
 HEADERS = ["common.cuh"]

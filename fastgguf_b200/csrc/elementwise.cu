@@ -457,3 +457,30 @@ extern "C" int fg_decode_advance(int *tokens, int *positions, const int *next_to
     if (B <= 0) return 0;
     return fg_launch(decode_advance_kernel, dim3((B + 127) / 128), dim3(128), 0, stream, tokens, positions, next_tokens, active, B);
 }
+
+// ------------------------------------------------------------------ two float32 matrices side by side
+// out[m, 0 .. E) = a[m, :], out[m, E .. 2 E) = b[m, :], in the contraction's input dtype
+template <typename T>
+__global__ void concat2_kernel(const float *__restrict__ a, int lda, const float *__restrict__ b, int ldb, T *__restrict__ out, int ldo,
+                               size_t total, int E) {
+    pdl_launch_dependents();
+    pdl_wait();
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; i < total; i += stride) {
+        size_t m = i / (2 * (size_t)E);
+        int c = (int)(i - m * 2 * (size_t)E);
+        out[m * ldo + c] = from_f32<T>(c < E ? a[m * lda + c] : b[m * ldb + c - E]);
+    }
+}
+
+extern "C" int fg_concat2(const float *a, int lda, const float *b, int ldb, void *out, int out_dtype, int ldo, int M, int E,
+                          cudaStream_t stream) {
+    size_t total = (size_t)M * 2 * (size_t)E;
+    if (total == 0) return 0;
+    size_t want = (total + 255) / 256;
+    int blocks = (int)(want > 148 * 16 ? 148 * 16 : want);
+    if (out_dtype == FG_F32) return fg_launch(concat2_kernel<float>, dim3(blocks), dim3(256), 0, stream, a, lda, b, ldb, (float *)out, ldo, total, E);
+    if (out_dtype == FG_BF16) return fg_launch(concat2_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, a, lda, b, ldb, (bf16 *)out, ldo, total, E);
+    return FG_ERR_BAD_DTYPE;
+}

@@ -40,6 +40,8 @@ int fg_norm_add_norm(const float *t, const float *w_post, float *x, const float 
                      int M, int E, float eps_post, float eps_next, cudaStream_t stream);
 int fg_activation(void *z, int dtype, long long total, int kind /* 0: relu(z)^2 */, cudaStream_t stream);
 int fg_softcap(float *logits, int R, int V, int ld, float cap, cudaStream_t stream);
+int fg_concat2(const float *a, int lda, const float *b, int ldb, void *out, int out_dtype, int ldo, int M, int E,
+               cudaStream_t stream);
 int fg_silu_mul(const void *gu, void *out, int dtype, int M, int F, cudaStream_t stream);
 int fg_decode_advance(int *tokens, int *positions, const int *next_tokens, const int *active, int B, cudaStream_t stream);
 int fg_gemm_generic(const void *A, int a_dtype, int lda, const void *W, int w_dtype, int ldw, void *C, int out_dtype,
@@ -49,6 +51,13 @@ int fg_attention_generic(const void *q, int ldq, void *out, int ldo, int dtype, 
                          const void *v_pool, int M, int H, int KV, int hd, int page_size, float scale, int window,
                          cudaStream_t stream);
 /* the same with values of head size hdv and, with a window, the sequence's first keep_first keys visible as well */
+/* softcap > 0: scores capped by softcap * tanh(score / softcap); sinks: a float per query head that joins the softmax's denominator;
+   latent: the cache holds a latent (v_pool, hdv numbers, also the value) and a rotated key part (k_pool, hd numbers) a position,
+   and a query head has hdv + hd numbers */
+int fg_attention_generic_ext(const void *q, int ldq, void *out, int ldo, int dtype, const int *positions,
+                             const int *row_seq, const int *block_table, int table_width, const void *k_pool,
+                             const void *v_pool, int M, int H, int KV, int hd, int hdv, int page_size, float scale,
+                             int window, int keep_first, float softcap, const float *sinks, int latent, cudaStream_t stream);
 int fg_attention_generic_kept(const void *q, int ldq, void *out, int ldo, int dtype, const int *positions,
                               const int *row_seq, const int *block_table, int table_width, const void *k_pool,
                               const void *v_pool, int M, int H, int KV, int hd, int hdv, int page_size, float scale,
@@ -70,6 +79,34 @@ int fg_retention_chunked(const float *proj, int ld, void *out, int out_dtype, in
                          const int *cu_rows, const int *slots, const float *cos_t, const float *sin_t,
                          const float *decay, float *state, int *plan, float *U, int n_seq, int n_chunks, int H, int dk,
                          int dv, float k_scale, float eps, cudaStream_t stream);
+/* gated linear attention (gla.cu): proj rows q [H, dk] | k [H, dk] | v [H, dv] | g [H, dv] float32, z rows [H, dk] decay logits
+   without their bias; state [slots, H, dk, dv] float32; out [M, H * dv] */
+int fg_gla(const float *proj, int ld, const float *z, int ldz, const float *z_bias, const float *norm_w, void *out, int out_dtype,
+           int ldo, const int *cu_rows, const int *slots, float *state, int n_seq, int H, int dk, int dv, float tau, float q_scale,
+           float eps, cudaStream_t stream);
+int fg_gla_chunk_tokens(void);
+int fg_gla_chunked_ok(int dk, int dv);
+int fg_gla_chunked(const float *proj, int ld, const float *z, int ldz, const float *z_bias, const float *norm_w, void *out,
+                   int out_dtype, int ldo, const int *cu_rows, const int *slots, float *state, int *plan, float *U, float *D,
+                   int n_seq, int n_chunks, int H, int dk, int dv, float tau, float q_scale, float eps, cudaStream_t stream);
+/* between an attention mixer's projections and its attention kernel (attention_prep.cu) */
+int fg_qkv_prepare(const float *proj, int ld, const float *bias, const float *conv_w, int taps, const float *conv_state,
+                   const float *qn_w, const float *kn_w, float eps, const float *cos_t, const float *sin_t, int tbl_half,
+                   int rot_dims, const int *positions, const int *row_seq, const int *cu_rows, const int *slots,
+                   const int *block_table, int table_width, void *q_out, int ldq, void *k_pool, void *v_pool, int dtype, int M,
+                   int H, int KV, int hd, int hdv, int page_size, cudaStream_t stream);
+int fg_conv_state_update(const float *proj, int ld, const float *bias, int taps, float *conv_state, const int *cu_rows,
+                         const int *slots, int n_seq, int C, cudaStream_t stream);
+int fg_latent_append(const float *kv, int ld, const float *norm_w, float eps, const float *cos_t, const float *sin_t, int tbl_half,
+                     const int *positions, const int *row_seq, const int *block_table, int table_width, void *k_pool,
+                     void *v_pool, int dtype, int M, int rank, int rot_dim, int page_size, cudaStream_t stream);
+int fg_rope_pairs(const float *in, int ld_in, int in_stride, int in_off, void *out, int out_dtype, int ld_out, int out_stride,
+                  int out_off, const int *positions, const float *cos_t, const float *sin_t, int tbl_half, int M, int H, int dims,
+                  cudaStream_t stream);
+int fg_rmsnorm_strided(const float *x, int ldx, const float *w, void *out, int out_dtype, int ldo, int R, int E, float eps,
+                       cudaStream_t stream);
+int fg_head_gemm(const void *A, int a_dtype, int lda, int a_stride, const void *W, int w_dtype, int ldw, int transposed, void *C,
+                 int c_dtype, int ldc, int c_stride, const float *gate, int ldg, int M, int N, int K, int H, cudaStream_t stream);
 int fg_moe_logits(const void *x, int ldx, const void *W, int ldw, int dtype, float *z, int M, int X, int E, cudaStream_t stream);
 int fg_moe_gather(const void *x, int ldx, int dtype, const int *order, int top, void *xs, int P, int E, cudaStream_t stream);
 int fg_moe_act(const float *gu, const int *order, const float *pair_weight, void *y, int dtype, int P, int F, float limit,

@@ -65,6 +65,7 @@ extern "C" {
 #define FG_ROLE_BLOCK 4
 #define FG_ROLE_EMBEDDING 5
 #define FG_ROLE_HEAD 6
+#define FG_ROLE_STREAM_MAP 7   /* built-in kinds only: a map of the residual stream that also reads the embedding's output */
 
 typedef struct fg_tensor_decl {
     char name[96];           /* the part's local tensor name */

@@ -1,0 +1,301 @@
+// Gated linear attention: linear attention whose state decays per KEY CHANNEL by a factor that depends on the token.
+//
+// Per head, with q_t, k_t of size dk, v_t of size dv and a decay a_t in (0, 1)^dk:
+//     a_t = sigmoid(z_t)^(1 / tau),  z_t = (low-rank projection of the token) + bias
+//     S_t = diag(a_t) S_(t-1) + k_t v_t^T          (S: [dk, dv], zero at the start of a sequence)
+//     o_t = S_t^T (q_t * q_scale)
+//     y_t = o_t / sqrt(mean(o_t^2) + eps) * w * silu(g_t)       (w: [dv], the same for every head)
+// The state, the decays (through log sigmoid, so that no power of a small number is formed), the sums, the unit norm and
+// the gate are 32-bit in every engine dtype; S lives in the engine's per-sequence state rows [slot, H, dk, dv].
+//
+// A row of `proj` holds a token's projections q [H, dk] | k [H, dk] | v [H, dv] | g [H, dv] as float32; a row of `z` the
+// decay logits [H, dk] WITHOUT their bias.
+//
+// Two forms:
+//   * gla_seq_kernel: one block per (sequence, head) walks its tokens one after another with S in shared memory
+//     (a decode step, short portions).
+//   * the chunked form for long portions, over chunks of GC tokens of all sequences and heads at once.  With
+//     b_t = sum_(s <= t) log a_s inside the chunk (all exponents below are <= 0, so nothing can overflow):
+//       1. U_c = sum_j (k_j * exp(b_n - b_j)) v_j^T,  D_c = exp(b_n)      what chunk c (n tokens) adds, and its decay
+//       2. S_c = diag(D_c) S_(c-1) + U_c, chunk after chunk               (U_c is overwritten by the state BEFORE c)
+//       3. o_t = S_(c-1)^T (q_t * exp(b_t)) + sum_(j <= t) (sum_i q_t[i] k_j[i] exp(b_t[i] - b_j[i])) v_j, norm, gate
+//     These are the recurrence's own terms in another order; nothing is approximated.
+#include "common.cuh"
+
+#define GLA_THREADS 256
+#define GC 16                       // tokens a chunk
+
+__device__ __forceinline__ float gla_silu(float z) { return z / (1.0f + expf(-z)); }
+// log(sigmoid(z)) = min(z, 0) - log(1 + exp(-|z|))
+__device__ __forceinline__ float log_sigmoid(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
+
+template <typename TO>
+__global__ void __launch_bounds__(GLA_THREADS)
+gla_seq_kernel(const float *__restrict__ proj, int ld, const float *__restrict__ z, int ldz, const float *__restrict__ z_bias,
+               const float *__restrict__ norm_w, TO *__restrict__ out, int ldo, const int *__restrict__ cu_rows,
+               const int *__restrict__ slots, float *__restrict__ state, int H, int dk, int dv, float inv_tau, float q_scale,
+               float eps) {
+    extern __shared__ float sm[];
+    __shared__ float scratch[32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int seq = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+    const int row0 = cu_rows[seq], row1 = cu_rows[seq + 1];
+    if (row1 <= row0) return;
+    const int G = GLA_THREADS / dv, n_active = G * dv;      // threads (g, j): column j of S, rows g, g + G, ...
+    float *S = sm, *qs = S + dk * dv, *ks = qs + dk, *as = ks + dk, *vs = as + dk, *part = vs + dv;
+    float *Sg = state + ((size_t)slots[seq] * H + h) * dk * dv;
+    for (int e = tid; e < dk * dv; e += GLA_THREADS) S[e] = Sg[e];
+    for (int r = row0; r < row1; r++) {
+        const float *row = proj + (size_t)r * ld;
+        for (int i = tid; i < dk; i += GLA_THREADS) {
+            qs[i] = row[(size_t)h * dk + i] * q_scale;
+            ks[i] = row[(size_t)(H + h) * dk + i];
+            as[i] = expf(log_sigmoid(z[(size_t)r * ldz + (size_t)h * dk + i] + z_bias[(size_t)h * dk + i]) * inv_tau);
+        }
+        for (int j = tid; j < dv; j += GLA_THREADS) vs[j] = row[(size_t)2 * H * dk + (size_t)h * dv + j];
+        __syncthreads();
+        if (tid < n_active) {
+            const int j = tid % dv, g = tid / dv;
+            const float vj = vs[j];
+            float acc = 0.f;
+            for (int i = g; i < dk; i += G) {
+                float s = fmaf(S[i * dv + j], as[i], ks[i] * vj);
+                S[i * dv + j] = s;
+                acc = fmaf(s, qs[i], acc);
+            }
+            part[g * dv + j] = acc;
+        }
+        __syncthreads();
+        float o = 0.f;
+        if (tid < dv)
+            for (int g = 0; g < G; g++) o += part[g * dv + tid];
+        float ss = block_sum(tid < dv ? o * o : 0.f, scratch);
+        if (tid < dv) {
+            float gate = row[(size_t)2 * H * dk + (size_t)(H + h) * dv + tid];
+            out[(size_t)r * ldo + (size_t)h * dv + tid] = from_f32<TO>(o * (1.0f / sqrtf(ss / (float)dv + eps)) * norm_w[tid] * gla_silu(gate));
+        }
+    }
+    __syncthreads();
+    for (int e = tid; e < dk * dv; e += GLA_THREADS) Sg[e] = S[e];
+}
+
+// ------------------------------------------------------------------ chunked form
+// Chunk c covers tokens [chunk_row[c], chunk_row[c] + chunk_len[c]); the chunks of a sequence are consecutive and in order,
+// sequence s owning chunks [seq_chunk0[s], seq_chunk0[s + 1]).  The plan is made on the device from the step's row offsets.
+__global__ void gla_chunk_plan_kernel(const int *__restrict__ cu_rows, int n_seq, int *__restrict__ chunk_row, int *__restrict__ chunk_len,
+                                      int *__restrict__ seq_chunk0) {
+    pdl_launch_dependents();
+    pdl_wait();
+    if (threadIdx.x == 0) {
+        int at = 0;
+        for (int s = 0; s < n_seq; s++) { seq_chunk0[s] = at; at += (cu_rows[s + 1] - cu_rows[s] + GC - 1) / GC; }
+        seq_chunk0[n_seq] = at;
+    }
+    __syncthreads();
+    for (int s = threadIdx.x; s < n_seq; s += blockDim.x) {
+        const int r0 = cu_rows[s], r1 = cu_rows[s + 1];
+        int c = seq_chunk0[s];
+        for (int r = r0; r < r1; r += GC, c++) { chunk_row[c] = r; chunk_len[c] = min(GC, r1 - r); }
+    }
+}
+
+// b[t][i] = sum_(s <= t) log a_s[i] for the chunk's tokens, into shared memory (row stride dk); one thread a channel
+__device__ __forceinline__ void gla_cumulative_log_decay(const float *__restrict__ z, int ldz, const float *__restrict__ z_bias, int r0, int n,
+                                                         int h, int dk, float inv_tau, float *b, int tid) {
+    for (int i = tid; i < dk; i += GLA_THREADS) {
+        const float bias = z_bias[(size_t)h * dk + i];
+        float run = 0.f;
+        for (int t = 0; t < n; t++) {
+            run += log_sigmoid(z[(size_t)(r0 + t) * ldz + (size_t)h * dk + i] + bias) * inv_tau;
+            b[t * dk + i] = run;
+        }
+    }
+}
+
+// 1. U[c, h] = sum_j (k_j * exp(b_n - b_j)) v_j^T and D[c, h] = exp(b_n).  One block per (chunk, head).
+__global__ void __launch_bounds__(GLA_THREADS)
+gla_chunk_state_kernel(const float *__restrict__ proj, int ld, const float *__restrict__ z, int ldz, const float *__restrict__ z_bias,
+                       const int *__restrict__ chunk_row, const int *__restrict__ chunk_len, float *__restrict__ U, float *__restrict__ D,
+                       int H, int dk, int dv, float inv_tau) {
+    extern __shared__ float sm[];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int c = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+    const int r0 = chunk_row[c], n = chunk_len[c];
+    float *b = sm, *kd = b + GC * dk, *vs = kd + GC * dk;      // [GC][dk], [GC][dk], [GC][dv]
+    gla_cumulative_log_decay(z, ldz, z_bias, r0, n, h, dk, inv_tau, b, tid);
+    for (int e = tid; e < n * dv; e += GLA_THREADS) {
+        const int t = e / dv, j = e - t * dv;
+        vs[e] = proj[(size_t)(r0 + t) * ld + (size_t)2 * H * dk + (size_t)h * dv + j];
+    }
+    __syncthreads();
+    for (int e = tid; e < n * dk; e += GLA_THREADS) {
+        const int t = e / dk, i = e - t * dk;
+        kd[e] = proj[(size_t)(r0 + t) * ld + (size_t)(H + h) * dk + i] * expf(b[(n - 1) * dk + i] - b[e]);
+    }
+    for (int i = tid; i < dk; i += GLA_THREADS) D[((size_t)c * H + h) * dk + i] = expf(b[(n - 1) * dk + i]);
+    __syncthreads();
+    float *Uc = U + ((size_t)c * H + h) * dk * dv;
+    for (int e = tid; e < dk * dv; e += GLA_THREADS) {
+        const int i = e / dv, j = e - i * dv;
+        float acc = 0.f;
+        for (int t = 0; t < n; t++) acc = fmaf(kd[t * dk + i], vs[t * dv + j], acc);
+        Uc[e] = acc;
+    }
+}
+
+// 2. per (sequence, head, slice of the state): S <- D_c S + U_c over the sequence's chunks; U_c receives the state before c
+__global__ void __launch_bounds__(GLA_THREADS)
+gla_chunk_scan_kernel(float *__restrict__ U, const float *__restrict__ D, const int *__restrict__ seq_chunk0, const int *__restrict__ slots,
+                      float *__restrict__ state, int H, int dk, int dv) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int seq = blockIdx.x, h = blockIdx.y;
+    const int e = blockIdx.z * GLA_THREADS + threadIdx.x;
+    if (e >= dk * dv) return;
+    const int i = e / dv;
+    const int c0 = seq_chunk0[seq], c1 = seq_chunk0[seq + 1];
+    float *Sg = state + ((size_t)slots[seq] * H + h) * dk * dv;
+    float s = Sg[e];
+    for (int c = c0; c < c1; c++) {
+        float *Uc = U + ((size_t)c * H + h) * dk * dv;
+        const float u = Uc[e], d = D[((size_t)c * H + h) * dk + i];
+        Uc[e] = s;
+        s = fmaf(s, d, u);
+    }
+    Sg[e] = s;
+}
+
+// 3. outputs of a chunk.  One block per (chunk, head); P (= U after the scan) is the state in front of the chunk.
+template <typename TO>
+__global__ void __launch_bounds__(GLA_THREADS)
+gla_chunk_out_kernel(const float *__restrict__ proj, int ld, const float *__restrict__ z, int ldz, const float *__restrict__ z_bias,
+                     const float *__restrict__ norm_w, TO *__restrict__ out, int ldo, const int *__restrict__ chunk_row,
+                     const int *__restrict__ chunk_len, const float *__restrict__ P, int H, int dk, int dv, float inv_tau, float q_scale,
+                     float eps) {
+    extern __shared__ float sm[];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int c = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+    const int r0 = chunk_row[c], n = chunk_len[c];
+    float *b = sm, *qs = b + GC * dk, *ks = qs + GC * dk, *vs = ks + GC * dk, *A = vs + GC * dv, *os = A + GC * GC, *inv = os + GC * dv;
+    gla_cumulative_log_decay(z, ldz, z_bias, r0, n, h, dk, inv_tau, b, tid);
+    for (int e = tid; e < n * dk; e += GLA_THREADS) {
+        const int t = e / dk, i = e - t * dk;
+        const float *row = proj + (size_t)(r0 + t) * ld;
+        qs[e] = row[(size_t)h * dk + i] * q_scale;
+        ks[e] = row[(size_t)(H + h) * dk + i];
+    }
+    for (int e = tid; e < n * dv; e += GLA_THREADS) {
+        const int t = e / dv, j = e - t * dv;
+        vs[e] = proj[(size_t)(r0 + t) * ld + (size_t)2 * H * dk + (size_t)h * dv + j];
+    }
+    __syncthreads();
+    // scores inside the chunk: A[t][j] = sum_i q_t[i] k_j[i] exp(b_t[i] - b_j[i]) for j <= t; a warp per pair
+    const int warp = tid >> 5, lane = tid & 31;
+    for (int pair = warp; pair < n * n; pair += GLA_THREADS / 32) {
+        const int t = pair / n, j = pair - t * n;
+        if (j > t) continue;
+        float acc = 0.f;
+        for (int i = lane; i < dk; i += 32) acc = fmaf(qs[t * dk + i] * ks[j * dk + i], expf(b[t * dk + i] - b[j * dk + i]), acc);
+        acc = warp_sum(acc);
+        if (lane == 0) A[t * GC + j] = acc;
+    }
+    // the carried part reads q_t * exp(b_t)
+    __syncthreads();
+    for (int e = tid; e < n * dk; e += GLA_THREADS) qs[e] *= expf(b[e]);
+    __syncthreads();
+    const float *Pc = P + ((size_t)c * H + h) * dk * dv;
+    for (int e = tid; e < n * dv; e += GLA_THREADS) {
+        const int t = e / dv, j = e - t * dv;
+        float acc = 0.f;
+        for (int i = 0; i < dk; i++) acc = fmaf(Pc[(size_t)i * dv + j], qs[t * dk + i], acc);
+        for (int u = 0; u <= t; u++) acc = fmaf(A[t * GC + u], vs[u * dv + j], acc);
+        os[e] = acc;
+    }
+    __syncthreads();
+    for (int t = warp; t < n; t += GLA_THREADS / 32) {
+        float ss = 0.f;
+        for (int j = lane; j < dv; j += 32) ss = fmaf(os[t * dv + j], os[t * dv + j], ss);
+        ss = warp_sum(ss);
+        if (lane == 0) inv[t] = 1.0f / sqrtf(ss / (float)dv + eps);
+    }
+    __syncthreads();
+    for (int e = tid; e < n * dv; e += GLA_THREADS) {
+        const int t = e / dv, j = e - t * dv;
+        const float gate = proj[(size_t)(r0 + t) * ld + (size_t)2 * H * dk + (size_t)(H + h) * dv + j];
+        out[(size_t)(r0 + t) * ldo + (size_t)h * dv + j] = from_f32<TO>(os[e] * inv[t] * norm_w[j] * gla_silu(gate));
+    }
+}
+
+static FgPerDevice g_gla_seq_setup[2], g_gla_state_setup, g_gla_out_setup[2];
+
+static size_t gla_seq_smem(int dk, int dv) { return ((size_t)dk * dv + 3 * dk + dv + (size_t)(GLA_THREADS / dv) * dv) * sizeof(float); }
+static size_t gla_state_smem(int dk, int dv) { return ((size_t)2 * GC * dk + (size_t)GC * dv) * sizeof(float); }
+static size_t gla_out_smem(int dk, int dv) { return ((size_t)3 * GC * dk + (size_t)2 * GC * dv + GC * GC + GC) * sizeof(float); }
+
+extern "C" int fg_gla_chunk_tokens(void) { return GC; }
+
+extern "C" int fg_gla(const float *proj, int ld, const float *z, int ldz, const float *z_bias, const float *norm_w, void *out, int out_dtype,
+                      int ldo, const int *cu_rows, const int *slots, float *state, int n_seq, int H, int dk, int dv, float tau, float q_scale,
+                      float eps, cudaStream_t stream) {
+    if (n_seq <= 0) return 0;
+    if (dk <= 0 || dv <= 0 || dv > GLA_THREADS || H <= 0 || H > 65535 || !(tau > 0.f)) return FG_ERR_BAD_SIZE;
+    const size_t smem = gla_seq_smem(dk, dv);
+    if (smem > 200 * 1024) return FG_ERR_BAD_SIZE;
+    if (out_dtype != FG_F32 && out_dtype != FG_BF16) return FG_ERR_BAD_DTYPE;
+    const bool wide = out_dtype == FG_F32;
+    if (fg_needs_setup(g_gla_seq_setup[wide ? 0 : 1])) {
+        cudaError_t e = wide ? cudaFuncSetAttribute(gla_seq_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)
+                             : cudaFuncSetAttribute(gla_seq_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (e != cudaSuccess) return (int)e;
+    }
+    if (wide)
+        return fg_launch(gla_seq_kernel<float>, dim3(n_seq, H), dim3(GLA_THREADS), smem, stream, proj, ld, z, ldz, z_bias, norm_w, (float *)out,
+                         ldo, cu_rows, slots, state, H, dk, dv, 1.0f / tau, q_scale, eps);
+    return fg_launch(gla_seq_kernel<bf16>, dim3(n_seq, H), dim3(GLA_THREADS), smem, stream, proj, ld, z, ldz, z_bias, norm_w, (bf16 *)out, ldo,
+                     cu_rows, slots, state, H, dk, dv, 1.0f / tau, q_scale, eps);
+}
+
+// 1 if the chunked form takes these sizes
+extern "C" int fg_gla_chunked_ok(int dk, int dv) {
+    if (dk <= 0 || dv <= 0) return 0;
+    return gla_state_smem(dk, dv) <= 200 * 1024 && gla_out_smem(dk, dv) <= 200 * 1024;
+}
+
+// n_chunks = sum over sequences of ceil(rows / fg_gla_chunk_tokens()).  plan: scratch of 2 * n_chunks + n_seq + 1 ints;
+// U: scratch [n_chunks, H, dk, dv] float32; D: scratch [n_chunks, H, dk] float32.
+extern "C" int fg_gla_chunked(const float *proj, int ld, const float *z, int ldz, const float *z_bias, const float *norm_w, void *out,
+                              int out_dtype, int ldo, const int *cu_rows, const int *slots, float *state, int *plan, float *U, float *D,
+                              int n_seq, int n_chunks, int H, int dk, int dv, float tau, float q_scale, float eps, cudaStream_t stream) {
+    if (n_seq <= 0 || n_chunks <= 0) return 0;
+    if (!fg_gla_chunked_ok(dk, dv) || H <= 0 || H > 65535 || !(tau > 0.f)) return FG_ERR_BAD_SIZE;
+    if (out_dtype != FG_F32 && out_dtype != FG_BF16) return FG_ERR_BAD_DTYPE;
+    const bool wide = out_dtype == FG_F32;
+    if (fg_needs_setup(g_gla_state_setup)) {
+        cudaError_t e = cudaFuncSetAttribute(gla_chunk_state_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (e != cudaSuccess) return (int)e;
+    }
+    if (fg_needs_setup(g_gla_out_setup[wide ? 0 : 1])) {
+        cudaError_t e = wide ? cudaFuncSetAttribute(gla_chunk_out_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)
+                             : cudaFuncSetAttribute(gla_chunk_out_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (e != cudaSuccess) return (int)e;
+    }
+    int *chunk_row = plan, *chunk_len = plan + n_chunks, *seq_chunk0 = plan + 2 * n_chunks;
+    const float inv_tau = 1.0f / tau;
+    int code = fg_launch(gla_chunk_plan_kernel, dim3(1), dim3(n_seq >= 256 ? 256 : 32), 0, stream, cu_rows, n_seq, chunk_row, chunk_len, seq_chunk0);
+    if (code) return code;
+    code = fg_launch(gla_chunk_state_kernel, dim3(n_chunks, H), dim3(GLA_THREADS), gla_state_smem(dk, dv), stream, proj, ld, z, ldz, z_bias,
+                     (const int *)chunk_row, (const int *)chunk_len, U, D, H, dk, dv, inv_tau);
+    if (code) return code;
+    code = fg_launch(gla_chunk_scan_kernel, dim3(n_seq, H, (dk * dv + GLA_THREADS - 1) / GLA_THREADS), dim3(GLA_THREADS), 0, stream, U,
+                     (const float *)D, (const int *)seq_chunk0, slots, state, H, dk, dv);
+    if (code) return code;
+    if (wide)
+        return fg_launch(gla_chunk_out_kernel<float>, dim3(n_chunks, H), dim3(GLA_THREADS), gla_out_smem(dk, dv), stream, proj, ld, z, ldz, z_bias,
+                         norm_w, (float *)out, ldo, (const int *)chunk_row, (const int *)chunk_len, (const float *)U, H, dk, dv, inv_tau, q_scale,
+                         eps);
+    return fg_launch(gla_chunk_out_kernel<bf16>, dim3(n_chunks, H), dim3(GLA_THREADS), gla_out_smem(dk, dv), stream, proj, ld, z, ldz, z_bias,
+                     norm_w, (bf16 *)out, ldo, (const int *)chunk_row, (const int *)chunk_len, (const float *)U, H, dk, dv, inv_tau, q_scale, eps);
+}

@@ -915,11 +915,12 @@ static std::map<std::string, ExpectedTensor> declared_tensors(const ModelSpec &s
         build(FG_ROLE_NORM, l.mixer_norm);
         if (l.has_feed_forward()) {
             build(FG_ROLE_FEED_FORWARD, l.feed_forward);
-            build(FG_ROLE_NORM, l.feed_forward_norm);
+            if (!l.feed_forward_norm.kind.empty()) build(FG_ROLE_NORM, l.feed_forward_norm);
         }
         if (!l.mixer_post_norm.kind.empty()) build(FG_ROLE_NORM, l.mixer_post_norm);
         if (!l.feed_forward_post_norm.kind.empty()) build(FG_ROLE_NORM, l.feed_forward_post_norm);
     }
+    if (!spec.reentry.kind.empty()) build(FG_ROLE_STREAM_MAP, spec.reentry);
     build(FG_ROLE_NORM, spec.final_norm);
     build(FG_ROLE_HEAD, spec.head);
     return out;

@@ -155,8 +155,10 @@ Json merge_generation_config(const std::string &model_dir, const Json &d) {
 // ------------------------------------------------------------------------------------ registry
 static std::mutex g_registry_mutex;
 std::unique_ptr<ModelConfig> zirivik_config_from_json(const Json &d);        // config_zirivik.cpp
+std::unique_ptr<ModelConfig> salulorn_config_from_json(const Json &d);       // config_salulorn.cpp
 static std::map<std::string, ConfigReader> &registry() {
-    static std::map<std::string, ConfigReader> r = {{"LlamaForCausalLM", &LlamaConfig::from_json}, {"Zirivik", &zirivik_config_from_json}};
+    static std::map<std::string, ConfigReader> r = {{"LlamaForCausalLM", &LlamaConfig::from_json}, {"Zirivik", &zirivik_config_from_json},
+                                                    {"Salulorn", &salulorn_config_from_json}};
     return r;
 }
 

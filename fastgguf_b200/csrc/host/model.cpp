@@ -44,7 +44,8 @@ ModelSpec ModelSpec::from_json(const Json &j) {
         ls.mixer_norm = part_spec_from_json(l.get("mixer_norm"), "mixer_norm");
         if (!l.get("feed_forward").is_null()) {                       // null or absent: a layer of a mixer alone
             ls.feed_forward = part_spec_from_json(l.get("feed_forward"), "feed_forward");
-            ls.feed_forward_norm = part_spec_from_json(l.get("feed_forward_norm"), "feed_forward_norm");
+            // a block whose sublayers share one norm (block "parallel") gives none for the feed-forward
+            if (!l.get("feed_forward_norm").is_null()) ls.feed_forward_norm = part_spec_from_json(l.get("feed_forward_norm"), "feed_forward_norm");
         } else if (!l.get("feed_forward_norm").is_null() || !l.get("feed_forward_post_norm").is_null())
             fail(FG_E_CONFIG, "model spec: a layer without a feed-forward has no norms for one");
         if (!l.get("mixer_post_norm").is_null()) ls.mixer_post_norm = part_spec_from_json(l.get("mixer_post_norm"), "mixer_post_norm");
@@ -58,11 +59,14 @@ ModelSpec ModelSpec::from_json(const Json &j) {
         else if (r.is_object() && r.get("layer").is_int()) {
             rs.layer = (int)r.get("layer").as_int();
             if (r.get("cache_from").is_int()) rs.cache_from = (int)r.get("cache_from").as_int();
+            rs.reenter = r.get("reenter").is_bool() && r.get("reenter").as_bool();
         } else fail(FG_E_CONFIG, "model spec: a schedule entry is {\"layer\": i, \"cache_from\": j or null}");
         s.schedule.push_back(rs);
     }
+    if (!j.get("reentry").is_null()) s.reentry = part_spec_from_json(j.get("reentry"), "reentry");
     for (size_t i = 0; i < s.schedule.size(); i++) {
         const RunSpec &run = s.schedule[i];
+        if (run.reenter && s.reentry.kind.empty()) fail(FG_E_CONFIG, format("schedule[%zu] asks for the reentry map, but the model spec has no 'reentry'", i));
         if (run.layer < 0 || run.layer >= (int)s.layers.size())
             fail(FG_E_CONFIG, format("schedule[%zu] names layer %d, but there are %zu layers", i, run.layer, s.layers.size()));
         if (run.cache_from >= 0) {
@@ -102,8 +106,11 @@ DecoderModel::DecoderModel(const ModelSpec &spec_, int dtype, int device, cudaSt
         Norm *n2 = nullptr, *p1 = nullptr, *p2 = nullptr;
         if (layer.has_feed_forward()) {
             ffn = dynamic_cast<FeedForward *>(build(FG_ROLE_FEED_FORWARD, layer.feed_forward));
-            n2 = dynamic_cast<Norm *>(build(FG_ROLE_NORM, layer.feed_forward_norm));
-            if (!ffn || !n2) fail(FG_E_INTERNAL, "a part was registered under the wrong role");
+            if (!layer.feed_forward_norm.kind.empty()) {
+                n2 = dynamic_cast<Norm *>(build(FG_ROLE_NORM, layer.feed_forward_norm));
+                if (!n2) fail(FG_E_INTERNAL, "a part was registered under the wrong role");
+            }
+            if (!ffn) fail(FG_E_INTERNAL, "a part was registered under the wrong role");
         }
         if (!layer.mixer_post_norm.kind.empty()) p1 = dynamic_cast<Norm *>(build(FG_ROLE_NORM, layer.mixer_post_norm));
         if (!layer.feed_forward_post_norm.kind.empty()) p2 = dynamic_cast<Norm *>(build(FG_ROLE_NORM, layer.feed_forward_post_norm));
@@ -114,6 +121,10 @@ DecoderModel::DecoderModel(const ModelSpec &spec_, int dtype, int device, cudaSt
         b->check_layer();
         blocks_.push_back(std::move(b));
         mixers_.push_back(mixer);
+    }
+    if (!spec.reentry.kind.empty()) {
+        reentry_ = dynamic_cast<StreamMap *>(build(FG_ROLE_STREAM_MAP, spec.reentry));
+        if (!reentry_) fail(FG_E_INTERNAL, "a part was registered under the wrong role");
     }
     final_norm_ = dynamic_cast<Norm *>(build(FG_ROLE_NORM, spec.final_norm));
     head_ = dynamic_cast<Head *>(build(FG_ROLE_HEAD, spec.head));
@@ -202,7 +213,9 @@ std::map<std::string, int> check_source(const TensorSource &source, const std::m
     for (auto &kv : expected) {
         const TensorInfo *t = source.find(kv.first);
         if (!t) continue;
-        if (t->shape != kv.second.shape)
+        bool fits = t->shape.size() == kv.second.shape.size();
+        for (size_t i = 0; fits && i < t->shape.size(); i++) fits = kv.second.shape[i] < 0 || kv.second.shape[i] == t->shape[i];
+        if (!fits)
             wrong.push_back(kv.first + " is " + shape_text(t->shape) + ", the configuration needs " + shape_text(kv.second.shape));
         else if (kv.second.is_int && dtype_is_float(t->dtype))
             wrong.push_back(kv.first + " is " + dtype_long_name(t->dtype) + ", an integer table is needed");
@@ -228,12 +241,15 @@ void DecoderModel::load_weights(const TensorSource *source, bool seed_random, ui
     DeviceBuffer raw;                                  // staging for tensors that need a conversion
     for (auto &kv : expected_) {
         const ExpectedTensor &e = kv.second;
+        // a size the declaration leaves open (-1) is the checkpoint's; random weights need every size declared
+        const std::vector<int64_t> &shape = seed_random ? e.shape : source->find(kv.first)->shape;
         int64_t rows = 1, cols = 1;
-        if (e.shape.size() == 1) cols = e.shape[0];
-        else if (e.shape.size() >= 2) {
-            cols = e.shape.back();
-            for (size_t i = 0; i + 1 < e.shape.size(); i++) rows *= e.shape[i];
+        if (shape.size() == 1) cols = shape[0];
+        else if (shape.size() >= 2) {
+            cols = shape.back();
+            for (size_t i = 0; i + 1 < shape.size(); i++) rows *= shape[i];
         }
+        if (rows < 0 || cols < 0) fail(FG_E_CONFIG, "tensor '" + kv.first + "' has a size that only a checkpoint can give; random weights need it in the configuration");
         Weight w;
         if (seed_random) {
             int dt = target_dtype(runtime.dtype, e.is_int, runtime.dtype);
@@ -454,15 +470,32 @@ Tensor DecoderModel::forward(Runtime &rt, const Batch &batch) {
     // the final norm can be started by the last block when the head takes every row as it is
     Norm *head_norm = (batch.want_all && bf16 && final_norm_->deferrable() && head_->supports_deferred_norm()) ? final_norm_ : nullptr;
     Tensor x = rt.arena->matrix(batch.n_rows, spec.hidden_size, FG_F32);      // the float32 residual stream
-    Norm *first = (n && !block_at(0)->finished_norms()) ? entry_norm(block_at(0)) : nullptr;
+    // an entry that the reentry map stands in front of reads a stream nobody has normalised yet
+    auto reenters = [&](size_t i) { return i < n && spec.schedule[i].reenter && reentry_; };
+    Norm *first = (n && !block_at(0)->finished_norms() && !reenters(0)) ? entry_norm(block_at(0)) : nullptr;
     DeferredNorm pending = embedding_->forward(rt, batch, x, first);
+    Tensor x0;                                     // the embedding's output, kept for the reentry map
+    bool any_reentry = false;
+    for (size_t i = 0; i < n; i++) any_reentry = any_reentry || reenters(i);
+    if (any_reentry && batch.n_rows > 0) {
+        x0 = rt.arena->matrix(batch.n_rows, spec.hidden_size, FG_F32);
+        FG_CUDA(cudaMemcpyAsync(x0.data, x.data, (size_t)batch.n_rows * spec.hidden_size * sizeof(float), cudaMemcpyDeviceToDevice, rt.stream));
+    }
     for (size_t i = 0; i < n; i++) {
-        Norm *next = i + 1 < n ? entry_norm(block_at(i + 1)) : head_norm;
+        if (reenters(i) && batch.n_rows > 0) {
+            Tensor fresh = rt.arena->matrix(batch.n_rows, spec.hidden_size, FG_F32);     // in the step's own lane: it outlives layers
+            reentry_->forward(rt, x, x0, fresh);
+            x = fresh;
+            pending = DeferredNorm();
+        }
+        Norm *next = i + 1 < n ? (reenters(i + 1) ? nullptr : entry_norm(block_at(i + 1))) : head_norm;
         // blocks that finish the next norm themselves hand it to a block of the same habit only (any dtype)
         if (block_at(i)->finished_norms()) next = (i + 1 < n && block_at(i + 1)->finished_norms()) ? block_at(i + 1)->mixer_norm : nullptr;
         else if (i + 1 < n && block_at(i + 1)->finished_norms()) next = nullptr;
+        if (reenters(i + 1)) next = nullptr;
         rt.arena->begin_layer((int)i);                 // this entry's temporaries reuse the memory of entry i - 2
         pending = block_at(i)->forward(rt, x, batch, io[i], pending, next);
+        rt.arena->end_layers();                        // what follows the block belongs to the step, not to the layer
     }
     rt.arena->end_layers();
     if (!batch.want_rows) return Tensor();

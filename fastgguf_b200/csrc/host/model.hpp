@@ -36,10 +36,12 @@ struct LayerSpec {
 struct RunSpec {
     int layer = 0;
     int cache_from = -1;                             // an EARLIER schedule entry whose cache this run reads
+    bool reenter = false;                            // the model's `reentry` map runs on the stream in front of this entry
 };
 struct ModelSpec {
     int64_t hidden_size = 0, vocab_size = 0, max_positions = 0;
     PartSpec embedding, final_norm, head;
+    PartSpec reentry;                                // optional (empty kind: none): x <- f(x, embedding output), see StreamMap
     std::vector<LayerSpec> layers;
     std::vector<RunSpec> schedule;
     std::vector<int> stop_token_ids;
@@ -116,6 +118,7 @@ private:
     Embedding *embedding_ = nullptr;
     Head *head_ = nullptr;
     Norm *final_norm_ = nullptr;
+    StreamMap *reentry_ = nullptr;
     std::vector<std::unique_ptr<Block>> blocks_;     // per layer
     std::vector<Mixer *> mixers_;                    // per layer
     std::map<std::string, ExpectedTensor> expected_;

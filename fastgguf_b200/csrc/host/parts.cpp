@@ -13,8 +13,8 @@ static const int EPI_BF16 = 0, EPI_F32 = 1, EPI_ADD_F32 = 2, EPI_SILU_MUL = 3;
 static const int KERNEL_BAD_SIZE = 10002;
 
 const char *role_name(int role) {
-    static const char *n[] = {"norm", "position", "mixer", "feed_forward", "block", "embedding", "head"};
-    return role >= 0 && role <= 6 ? n[role] : "?";
+    static const char *n[] = {"norm", "position", "mixer", "feed_forward", "block", "embedding", "head", "stream_map"};
+    return role >= 0 && role <= 7 ? n[role] : "?";
 }
 
 // ------------------------------------------------------------------------------------ parameters
@@ -384,8 +384,25 @@ std::vector<double> rotary_divisors(int rotary_dim, double theta, const Json &sc
     if (!scaling.is_object()) return div;
     const Json &kind = scaling.get("rope_type");
     if (kind.is_null() || (kind.is_string() && kind.as_string() == "default")) return div;
+    if (kind.is_string() && kind.as_string() == "yarn") {
+        // Frequencies between two wavelengths are blended from "as trained" to "slowed by factor".  With
+        // dim(t) = n_rot ln(orig / (2 pi t)) / (2 ln theta) - the (fractional) rotary dimension whose wave turns t times over
+        // the original length - lo = max(floor(dim(beta_fast)), 0), hi = min(ceil(dim(beta_slow)), n_rot - 1) and
+        // ramp_j = clamp((j - lo) / max(hi - lo, 0.001), 0, 1), pair j's frequency is f_j / factor * ramp_j + f_j (1 - ramp_j).
+        double factor = param_float(scaling, "factor", "rope scaling"), orig = param_float(scaling, "original_max_position_embeddings", "rope scaling");
+        double fast = param_float(scaling, "beta_fast", "rope scaling"), slow = param_float(scaling, "beta_slow", "rope scaling");
+        if (!(factor > 0) || !(orig > 0) || !(fast > 0) || !(slow > 0) || !(theta > 1)) fail(FG_E_CONFIG, "rope scaling yarn: factor, original length and betas must be positive");
+        const double two_pi = 2.0 * 3.14159265358979323846;
+        auto dim_of = [&](double turns) { return rotary_dim * std::log(orig / (two_pi * turns)) / (2.0 * std::log(theta)); };
+        double lo = std::max(std::floor(dim_of(fast)), 0.0), hi = std::min(std::ceil(dim_of(slow)), (double)rotary_dim - 1.0);
+        for (int j = 0; j < half; j++) {
+            double ramp = std::min(std::max((j - lo) / std::max(hi - lo, 0.001), 0.0), 1.0);
+            div[(size_t)j] = 1.0 / (ramp / factor + (1.0 - ramp));
+        }
+        return div;
+    }
     if (!kind.is_string() || kind.as_string() != "llama3")
-        fail(FG_E_CONFIG, "rotary scaling " + kind.dump() + " is not known (known: default, llama3)");
+        fail(FG_E_CONFIG, "rotary scaling " + kind.dump() + " is not known (known: default, llama3, yarn)");
     double factor = param_float(scaling, "factor", "rope scaling"), low = param_float(scaling, "low_freq_factor", "rope scaling");
     double high = param_float(scaling, "high_freq_factor", "rope scaling");
     double orig = param_float(scaling, "original_max_position_embeddings", "rope scaling");
@@ -401,6 +418,14 @@ std::vector<double> rotary_divisors(int rotary_dim, double theta, const Json &sc
         }
     }
     return div;
+}
+
+// yarn also stretches the rotated vectors: cos and sin are both multiplied by 0.1 ln(factor) + 1
+double rotary_amplitude(const Json &scaling) {
+    if (!scaling.is_object()) return 1.0;
+    const Json &kind = scaling.get("rope_type");
+    if (!kind.is_string() || kind.as_string() != "yarn") return 1.0;
+    return 0.1 * std::log(param_float(scaling, "factor", "rope scaling")) + 1.0;
 }
 
 class RotaryEncoding : public PositionEncoding {
@@ -439,12 +464,13 @@ public:
         std::vector<double> div = rotary_divisors(n_rot_, theta_, scaling_);
         std::vector<double> inv((size_t)rh);
         for (int j = 0; j < rh; j++) inv[(size_t)j] = std::pow(theta_, -2.0 * j / n_rot_) / div[(size_t)j];
+        const double amp = rotary_amplitude(scaling_);
         std::vector<float> c((size_t)max_positions * half), s((size_t)max_positions * half);
         for (int pos = 0; pos < max_positions; pos++) {
             for (int j = 0; j < half; j++) {
                 double ang = j < rh ? (double)pos * inv[(size_t)j] : 0.0;
-                c[(size_t)pos * half + j] = (float)std::cos(ang);
-                s[(size_t)pos * half + j] = (float)std::sin(ang);
+                c[(size_t)pos * half + j] = (float)((j < rh ? amp : 1.0) * std::cos(ang));
+                s[(size_t)pos * half + j] = (float)((j < rh ? amp : 1.0) * std::sin(ang));
             }
         }
         cos_ = make_weight(max_positions, half, FG_F32, "rotary tables");
@@ -758,6 +784,63 @@ public:
         rt.overwrite = false;
         return finished(join(feed_forward_post_norm, hand_over), hand_over);
     }
+};
+
+// ------------------------------------------------------------------------------------ parallel block
+// x += mixer(norm1(x)) + feed_forward(norm1(x)): ONE norm, both sublayers read its output, and both add their results to the
+// float32 stream (the mixer first).  In bfloat16 the started norm that the block before handed over serves both sublayers,
+// and the last sublayer's output projection starts the next block's norm.
+class ParallelBlock : public Block {
+public:
+    void check_layer() const override {
+        if (!mixer || !mixer_norm) fail(FG_E_CONFIG, "a layer needs a mixer and its norm");
+        if (feed_forward_norm || mixer_post_norm || feed_forward_post_norm)
+            fail(FG_E_CONFIG, "block 'parallel' has one norm, in front of both sublayers");
+    }
+    DeferredNorm forward(Runtime &rt, Tensor &x, const Batch &batch, const LayerIO &io, const DeferredNorm &pending,
+                         Norm *next_norm) override {
+        const bool bf16 = rt.dtype == FG_BF16;
+        const bool mixer_defers = bf16 && mixer->supports_deferred_norm();
+        const bool ffn_defers = bf16 && feed_forward && feed_forward->supports_deferred_norm();
+        const bool started = pending.defined() && pending.tiles > 0;
+        Tensor xn;                                   // the finished norm, made once if anybody needs it
+        auto finished = [&]() -> const Tensor & {
+            if (!xn.defined()) xn = !pending.defined() ? mixer_norm->forward(rt, x, nullptr, 0) : pending.tiles == 0 ? pending.xw : pending.materialize(rt);
+            return xn;
+        };
+        // both sublayers must have read the stream's norm before either adds to the stream: a finished norm is a copy, and a
+        // started one (xw and the row sums) is a copy as well, so the order of the two additions is free
+        DeferredNorm out;
+        Norm *mixer_emits = feed_forward ? nullptr : next_norm;
+        if (mixer_defers && started) out = mixer->forward(rt, Tensor(), &pending, batch, io, x, mixer_emits);
+        else out = mixer->forward(rt, finished(), nullptr, batch, io, x, mixer_defers ? mixer_emits : nullptr);
+        if (!feed_forward) return mixer_defers ? out : DeferredNorm();
+        if (ffn_defers && started) return feed_forward->forward(rt, Tensor(), &pending, batch, x, next_norm);
+        out = feed_forward->forward(rt, finished(), nullptr, batch, x, ffn_defers ? next_norm : nullptr);
+        return ffn_defers ? out : DeferredNorm();
+    }
+};
+
+// ------------------------------------------------------------------------------------ stream maps
+// out = W [x; x0]: the stream and the embedding's output side by side through one matrix [E, 2 E] (x's columns first).
+// The sum is 32-bit; in bfloat16 the two inputs are rounded for the contraction as every contraction's input is.
+class ConcatLinear : public StreamMap {
+public:
+    ConcatLinear(const Json &p) : E_(param_int(p, "hidden_size", "concat_linear")) {
+        if (E_ <= 0) fail(FG_E_CONFIG, "concat_linear: hidden_size must be positive");
+    }
+    std::vector<TensorDecl> tensor_decls() const override { return {{"weight", {E_, 2 * E_}}}; }
+    void load(const std::map<std::string, Weight> &tensors, Runtime &) override { w_ = Linear(tensor_of(tensors, "weight")); }
+    void forward(Runtime &rt, const Tensor &x, const Tensor &x0, Tensor &out) override {
+        const int64_t M = x.rows;
+        Tensor both = rt.arena->matrix(M, 2 * E_, rt.dtype);
+        FG_LAUNCH("core", fg_concat2, x.ptr<float>(), (int)x.ld, x0.ptr<float>(), (int)x0.ld, both.data, both.dtype, (int)both.ld, (int)M, (int)E_, rt.stream);
+        w_.forward(rt, both, nullptr, out, FG_F32, false, nullptr, nullptr);
+    }
+
+private:
+    int64_t E_;
+    Linear w_;
 };
 
 // ------------------------------------------------------------------------------------ embedding and head
@@ -1097,7 +1180,7 @@ public:
 // ------------------------------------------------------------------------------------ registries
 static std::mutex g_parts_mutex;
 static std::map<std::string, PartFactory> &factories(int role) {
-    static std::map<std::string, PartFactory> r[7];
+    static std::map<std::string, PartFactory> r[8];
     static bool init = false;
     if (!init) {
         init = true;
@@ -1107,15 +1190,18 @@ static std::map<std::string, PartFactory> &factories(int role) {
         r[FG_ROLE_FEED_FORWARD]["swiglu"] = [](Runtime &, const Json &p, BuildContext &) { return std::make_unique<SwiGLU>(p); };
         r[FG_ROLE_EMBEDDING]["embedding"] = [](Runtime &, const Json &p, BuildContext &) { return std::make_unique<TokenEmbedding>(p); };
         r[FG_ROLE_HEAD]["lm_head"] = [](Runtime &, const Json &p, BuildContext &) { return std::make_unique<LMHead>(p); };
+        r[FG_ROLE_STREAM_MAP]["concat_linear"] = [](Runtime &, const Json &p, BuildContext &) { return std::make_unique<ConcatLinear>(p); };
         add_recurrent_kinds(r[FG_ROLE_MIXER]);
+        add_attention_kinds(r[FG_ROLE_MIXER]);
         add_expert_kinds(r[FG_ROLE_FEED_FORWARD]);
     }
-    if (role < 0 || role > 6) fail(FG_E_USAGE, format("role %d does not exist", role));
+    if (role < 0 || role > 7) fail(FG_E_USAGE, format("role %d does not exist", role));
     return r[role];
 }
 static std::map<std::string, BlockFactory> &block_factories() {
     static std::map<std::string, BlockFactory> r = {{"prenorm", [](Runtime &) { return std::make_unique<PreNormBlock>(); }},
-                                                     {"sandwich", [](Runtime &) { return std::make_unique<SandwichBlock>(); }}};
+                                                     {"sandwich", [](Runtime &) { return std::make_unique<SandwichBlock>(); }},
+                                                     {"parallel", [](Runtime &) { return std::make_unique<ParallelBlock>(); }}};
     return r;
 }
 

@@ -180,6 +180,14 @@ public:
     virtual Tensor forward(Runtime &rt, const Tensor &xn, const DeferredNorm *deferred) = 0;
 };
 
+// A map of the residual stream between two schedule entries that also reads what the embedding produced: models that
+// run a span of layers several times feed the embedding's output back in at the start of every pass.
+class StreamMap : public Part {
+public:
+    // out [M, E] float32 (fresh memory) = f(x, x0); x: the stream, x0: the embedding's output, both [M, E] float32
+    virtual void forward(Runtime &rt, const Tensor &x, const Tensor &x0, Tensor &out) = 0;
+};
+
 // ---- registries, one per role
 struct BuildContext;                               // resolves nested parts (shared position encodings)
 using PartFactory = std::function<std::unique_ptr<Part>(Runtime &, const Json &params, BuildContext &)>;
@@ -199,6 +207,7 @@ void register_external_part(int role, const std::string &kind, const fg_part_vta
 
 // the built-in kinds that live in other files than parts.cpp (called once, under the registry's lock)
 void add_recurrent_kinds(std::map<std::string, PartFactory> &mixers);
+void add_attention_kinds(std::map<std::string, PartFactory> &mixers);
 void add_expert_kinds(std::map<std::string, PartFactory> &feed_forwards);
 
 // a part's tensor by its local name (an internal error if the model did not hand it over)
@@ -255,7 +264,9 @@ Tensor rope_attention(Runtime &rt, const Tensor &qkv, const Batch &batch, const 
                       const float *sin_t, const AttentionShape &shape);
 int decode_splits(int n_sm, int n_seq, int n_heads, int n_kv_heads, int table_width, int head_dim);
 
-// llama3 frequency divisors per rotary pair (all ones without scaling)
+// frequency divisors per rotary pair (all ones without scaling; kinds llama3 and yarn)
 std::vector<double> rotary_divisors(int rotary_dim, double theta, const Json &scaling);
+// the factor both cos and sin are multiplied by (1 unless the scaling kind has one)
+double rotary_amplitude(const Json &scaling);
 
 }  // namespace fg

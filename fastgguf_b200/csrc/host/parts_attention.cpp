@@ -1,0 +1,243 @@
+// Attention mixers beyond the plain grouped-query one of parts.cpp.  Both keep their keys and values in the engine's paged
+// cache, take their sizes and constants as parameters, and run the any-size attention kernel with its extensions (capped
+// scores, a sink in the softmax, keys that are a latent plus a rotated part); scores, softmax, norms and angles are 32-bit.
+//
+// "sink_attention": grouped-query attention with everything optional that sits between the projections and the scores -
+//     q = W_q h (+ b_q), k, v alike                                   biases
+//     a short causal convolution over time on every channel of q, k and v (weights [channels, taps]); the last taps - 1
+//       inputs of a sequence are fixed-size state, carried in the engine's state pool
+//     q <- q / sqrt(mean(q^2) + eps) * w over ALL of q's rows at once, k alike          ("qk_norm": "whole")
+//     rotation of the first rotary_dim numbers of each head, members (2i, 2i + 1) of a pair (position: a "rope" part)
+//     score = scale * (q . k), then softcap * tanh(score / softcap)
+//     a row sees itself and the window - 1 keys before it
+//     the softmax's denominator also holds exp(sink_h), a learned number per head
+//
+// "latent_attention": keys and values are linear maps of ONE small latent per token, c = norm(W_dkv h)[0:kv_rank], plus a
+// rotated key part of rot_dim numbers that all heads share; queries pass through a latent of their own,
+// q = W_uq norm(W_dq h), each head [head_dim unrotated | rot_dim rotated].  score = scale * (q_plain . (W_uk c) + q_rot . k_rot),
+// causal, a sink per head, the heads' outputs times sigmoid(W_g h), then W_o.  The cache holds c (in the value pool) and the
+// rotated part (in the key pool) only.  The key map is folded into the query, q_abs[h] = W_uk[h]^T q_plain[h], so that a score
+// is q_abs . c + q_rot . k_rot, and the value map is applied to the attention's output over the latents,
+// o[h] = W_uv[h] (sum_j p_j c_j): the same sums in another order, for prompts, portions and single tokens alike.
+#include <cmath>
+
+#include "parts.hpp"
+
+namespace fg {
+
+static bool flag(const Json &p, const char *key) { return p.get(key).is_bool() && p.get(key).as_bool(); }
+
+static Weight as_f32(const Weight &w, cudaStream_t s) { return w.t.dtype == FG_F32 ? w : concat_rows({w}, FG_F32, s); }
+
+class SinkAttention : public Mixer {
+public:
+    SinkAttention(const Json &p, BuildContext &ctx) {
+        const char *me = "sink_attention";
+        E_ = (int)param_int(p, "hidden_size", me);
+        H_ = (int)param_int(p, "n_heads", me);
+        KV_ = (int)param_int(p, "n_kv_heads", H_, me);
+        hd_ = (int)param_int(p, "head_dim", me);
+        hdv_ = (int)param_int(p, "v_head_dim", hd_, me);
+        if (E_ <= 0 || H_ <= 0 || KV_ <= 0 || hd_ <= 0 || hdv_ <= 0) fail(FG_E_CONFIG, "sink_attention: sizes must be positive");
+        if (H_ % KV_) fail(FG_E_CONFIG, format("sink_attention: %d heads are not a multiple of %d KV heads", H_, KV_));
+        scale_ = (float)param_float(p, "scale", 1.0 / std::sqrt((double)hd_), me);
+        window_ = (int)param_int(p, "window", 0, me);
+        softcap_ = (float)param_float(p, "softcap", 0.0, me);
+        taps_ = (int)param_int(p, "conv_taps", 0, me);
+        eps_ = (float)param_float(p, "eps", 1e-6, me);
+        bias_ = flag(p, "bias");
+        sink_ = flag(p, "sink");
+        const Json &qn = p.get("qk_norm");
+        if (!qn.is_null() && !(qn.is_string() && qn.as_string() == "whole")) fail(FG_E_CONFIG, "sink_attention: qk_norm " + qn.dump() + " is not known (known: whole)");
+        qk_norm_ = !qn.is_null();
+        if (window_ < 0 || softcap_ < 0.f || taps_ < 0) fail(FG_E_CONFIG, "sink_attention: window, softcap and conv_taps cannot be negative");
+        if (hdv_ > 512) fail(FG_E_CONFIG, format("sink_attention: v_head_dim %d exceeds 512, the largest the kernel takes", hdv_));
+        if (((size_t)H_ * hd_ + (size_t)KV_ * (hd_ + hdv_)) * 4 > 200 * 1024) fail(FG_E_CONFIG, "sink_attention: a token's q, k and v exceed what the kernel holds in shared memory");
+        const Json &pos = p.get("position");
+        if (!pos.is_null()) {
+            position_ = dynamic_cast<PositionEncoding *>(ctx.nested(FG_ROLE_POSITION, pos));
+            if (!position_) fail(FG_E_CONFIG, "sink_attention: 'position' is not a position encoding");
+            if (position_->head_dim() != hd_)
+                fail(FG_E_CONFIG, format("sink_attention: the position encoding is built for head_dim %d, the mixer has %d", position_->head_dim(), hd_));
+            rot_dims_ = (int)param_int(pos.get("params"), "rotary_dim", hd_, me);
+        }
+    }
+    std::vector<TensorDecl> tensor_decls() const override {
+        const int64_t Q = (int64_t)H_ * hd_, K = (int64_t)KV_ * hd_, V = (int64_t)KV_ * hdv_;
+        std::vector<TensorDecl> d = {{"q_proj.weight", {Q, E_}}, {"k_proj.weight", {K, E_}}, {"v_proj.weight", {V, E_}},
+                                     {"o_proj.weight", {E_, (int64_t)H_ * hdv_}}};
+        if (bias_) for (auto &n : std::vector<std::pair<const char *, int64_t>>{{"q_proj.bias", Q}, {"k_proj.bias", K}, {"v_proj.bias", V}}) d.push_back({n.first, {n.second}});
+        if (taps_ > 0)
+            for (auto &n : std::vector<std::pair<const char *, int64_t>>{{"q_conv.weight", Q}, {"k_conv.weight", K}, {"v_conv.weight", V}})
+                d.push_back({n.first, {n.second, (int64_t)taps_}, false, 0, 0.5f});
+        if (qk_norm_) { d.push_back({"q_norm.weight", {Q}, false, 1, 0.01f}); d.push_back({"k_norm.weight", {K}, false, 1, 0.01f}); }
+        if (sink_) d.push_back({"sinks", {(int64_t)H_}, false, 0, 1.0f});
+        return d;
+    }
+    bool cache_request(CacheRequest *out) const override {
+        out->n_kv_heads = KV_; out->head_dim = hd_; out->window = window_; out->v_head_dim = hdv_; out->keep_first = 0;
+        return true;
+    }
+    int64_t channels() const { return (int64_t)H_ * hd_ + (int64_t)KV_ * (hd_ + hdv_); }
+    int64_t state_bytes() const override { return taps_ > 1 ? (int64_t)(taps_ - 1) * channels() * (int64_t)sizeof(float) : 0; }
+    bool supports_deferred_norm() const override { return true; }
+    bool can_overwrite() const override { return true; }
+    void load(const std::map<std::string, Weight> &tensors, Runtime &rt) override {
+        const Weight &q = tensor_of(tensors, "q_proj.weight"), &k = tensor_of(tensors, "k_proj.weight"), &v = tensor_of(tensors, "v_proj.weight");
+        int dt = (q.t.dtype == k.t.dtype && k.t.dtype == v.t.dtype) ? q.t.dtype : FG_F32;
+        qkv_ = Linear(concat_rows({q, k, v}, dt, rt.stream));
+        o_ = Linear(tensor_of(tensors, "o_proj.weight"));
+        auto three = [&](const char *a, const char *b, const char *c, int64_t cols) {
+            Weight x = tensor_of(tensors, a), y = tensor_of(tensors, b), z = tensor_of(tensors, c);
+            // row-major [channels, cols]: the three lie one after another
+            Weight out = make_weight(x.t.numel() / cols + y.t.numel() / cols + z.t.numel() / cols, cols, FG_F32, "per-channel parameters of attention");
+            size_t at = 0;
+            for (const Weight *w : {&x, &y, &z}) {
+                dev_convert(w->t.data, w->t.dtype, (char *)out.t.data + at * 4, FG_F32, w->t.numel(), rt.stream);
+                at += (size_t)w->t.numel();
+            }
+            return out;
+        };
+        if (bias_) bias_w_ = three("q_proj.bias", "k_proj.bias", "v_proj.bias", 1);
+        if (taps_ > 0) conv_w_ = three("q_conv.weight", "k_conv.weight", "v_conv.weight", taps_);
+        if (qk_norm_) { qn_w_ = as_f32(tensor_of(tensors, "q_norm.weight"), rt.stream); kn_w_ = as_f32(tensor_of(tensors, "k_norm.weight"), rt.stream); }
+        if (sink_) sinks_w_ = as_f32(tensor_of(tensors, "sinks"), rt.stream);
+    }
+    void prepare(Runtime &rt, int max_positions) override { if (position_) position_->prepare(rt, max_positions); }
+    DeferredNorm forward(Runtime &rt, const Tensor &xn, const DeferredNorm *deferred, const Batch &b, const LayerIO &io, Tensor &residual,
+                         Norm *emit_norm) override {
+        if (io.group < 0 || !io.k_pool || !io.write_cache) fail(FG_E_INTERNAL, "sink_attention: the schedule entry has no cache of its own");
+        if (taps_ > 1 && (!io.state || io.state_bytes < state_bytes())) fail(FG_E_INTERNAL, "sink_attention: the schedule entry has no state rows");
+        const int *table = b.block_tables.at((size_t)io.group);
+        // the projections feed a convolution, a norm and a rotation: they stay float32 until those are done
+        Tensor proj = qkv_.forward(rt, xn, deferred, Tensor(), FG_F32, false, nullptr, nullptr);
+        const int M = (int)proj.rows;
+        Tensor q = rt.arena->matrix(M, (int64_t)H_ * hd_, rt.dtype);
+        const float *bias = bias_ ? bias_w_.t.ptr<float>() : nullptr;
+        FG_LAUNCH("mix", fg_qkv_prepare, proj.ptr<float>(), (int)proj.ld, bias, taps_ > 0 ? conv_w_.t.ptr<float>() : nullptr, taps_,
+                  (const float *)io.state, qk_norm_ ? qn_w_.t.ptr<float>() : nullptr, qk_norm_ ? kn_w_.t.ptr<float>() : nullptr, eps_,
+                  position_ ? position_->cos_table() : nullptr, position_ ? position_->sin_table() : nullptr, hd_ / 2, position_ ? rot_dims_ : 0,
+                  b.positions, b.row_seq, b.cu_rows, b.slots, table, b.table_width, q.data, (int)q.ld, io.k_pool, io.v_pool, rt.dtype, M, H_, KV_,
+                  hd_, hdv_, io.page_size, rt.stream);
+        if (taps_ > 1)
+            FG_LAUNCH("mix", fg_conv_state_update, proj.ptr<float>(), (int)proj.ld, bias, taps_, (float *)io.state, b.cu_rows, b.slots, b.n_seq,
+                      (int)channels(), rt.stream);
+        Tensor attn = rt.arena->matrix(M, (int64_t)H_ * hdv_, rt.dtype);
+        FG_LAUNCH("core", fg_attention_generic_ext, q.data, (int)q.ld, attn.data, (int)attn.ld, rt.dtype, b.positions, b.row_seq, table,
+                  b.table_width, io.k_pool, io.v_pool, M, H_, KV_, hd_, hdv_, io.page_size, scale_, window_, 0, softcap_,
+                  sink_ ? sinks_w_.t.ptr<float>() : nullptr, 0, rt.stream);
+        DeferredNorm started;
+        o_.forward(rt, attn, nullptr, residual, FG_F32, !rt.overwrite, emit_norm, &started);
+        return started;
+    }
+
+private:
+    int E_ = 0, H_ = 0, KV_ = 0, hd_ = 0, hdv_ = 0, window_ = 0, taps_ = 0, rot_dims_ = 0;
+    float scale_ = 1.f, softcap_ = 0.f, eps_ = 1e-6f;
+    bool bias_ = false, sink_ = false, qk_norm_ = false;
+    PositionEncoding *position_ = nullptr;
+    Linear qkv_, o_;
+    Weight bias_w_, conv_w_, qn_w_, kn_w_, sinks_w_;
+};
+
+class LatentAttention : public Mixer {
+public:
+    LatentAttention(const Json &p, BuildContext &ctx) {
+        const char *me = "latent_attention";
+        E_ = (int)param_int(p, "hidden_size", me);
+        H_ = (int)param_int(p, "n_heads", me);
+        d_ = (int)param_int(p, "head_dim", me);
+        dr_ = (int)param_int(p, "rot_dim", me);
+        dv_ = (int)param_int(p, "v_head_dim", d_, me);
+        r_ = (int)param_int(p, "kv_rank", me);
+        qr_ = (int)param_int(p, "q_rank", me);
+        if (E_ <= 0 || H_ <= 0 || d_ <= 0 || dr_ <= 0 || dv_ <= 0 || r_ <= 0 || qr_ <= 0) fail(FG_E_CONFIG, "latent_attention: sizes must be positive");
+        if (dr_ % 2) fail(FG_E_CONFIG, format("latent_attention: rot_dim must be even, got %d", dr_));
+        if (r_ > 512) fail(FG_E_CONFIG, format("latent_attention: kv_rank %d exceeds 512, the largest the kernel takes", r_));
+        scale_ = (float)param_float(p, "scale", 1.0 / std::sqrt((double)(d_ + dr_)), me);
+        eps_ = (float)param_float(p, "eps", 1e-6, me);
+        sink_ = flag(p, "sink");
+        gate_ = flag(p, "gate");
+        const Json &pos = p.get("position");
+        position_ = pos.is_null() ? nullptr : dynamic_cast<PositionEncoding *>(ctx.nested(FG_ROLE_POSITION, pos));
+        if (!position_) fail(FG_E_CONFIG, "latent_attention: 'position' must be a position encoding for the rotated part");
+        if (position_->head_dim() != dr_)
+            fail(FG_E_CONFIG, format("latent_attention: the position encoding is built for head_dim %d, the rotated part has %d", position_->head_dim(), dr_));
+    }
+    std::vector<TensorDecl> tensor_decls() const override {
+        const int64_t HV = (int64_t)H_ * dv_;
+        std::vector<TensorDecl> d = {{"q_down.weight", {qr_, E_}}, {"q_down_norm.weight", {qr_}, false, 1, 0.01f}, {"q_up.weight", {(int64_t)H_ * (d_ + dr_), qr_}},
+                                     {"kv_down.weight", {(int64_t)r_ + dr_, E_}}, {"kv_down_norm.weight", {r_}, false, 1, 0.01f},
+                                     {"k_up.weight", {(int64_t)H_ * d_, r_}}, {"v_up.weight", {HV, r_}}, {"o_proj.weight", {E_, HV}}};
+        if (gate_) d.push_back({"g_proj.weight", {HV, E_}});
+        if (sink_) d.push_back({"sinks", {(int64_t)H_}, false, 0, 1.0f});
+        return d;
+    }
+    bool cache_request(CacheRequest *out) const override {
+        // one "head" a position: the rotated key part in the key pool, the latent in the value pool
+        out->n_kv_heads = 1; out->head_dim = dr_; out->window = 0; out->v_head_dim = r_; out->keep_first = 0;
+        return true;
+    }
+    bool supports_deferred_norm() const override { return true; }
+    bool can_overwrite() const override { return true; }
+    void load(const std::map<std::string, Weight> &tensors, Runtime &rt) override {
+        const Weight &dq = tensor_of(tensors, "q_down.weight"), &dkv = tensor_of(tensors, "kv_down.weight");
+        std::vector<Weight> parts = {dq, dkv};
+        bool same = dq.t.dtype == dkv.t.dtype;
+        if (gate_) { parts.push_back(tensor_of(tensors, "g_proj.weight")); same = same && parts.back().t.dtype == dq.t.dtype; }
+        down_ = Linear(concat_rows(parts, same ? dq.t.dtype : FG_F32, rt.stream));
+        q_up_ = Linear(tensor_of(tensors, "q_up.weight"));
+        k_up_ = tensor_of(tensors, "k_up.weight");
+        v_up_ = tensor_of(tensors, "v_up.weight");
+        o_ = Linear(tensor_of(tensors, "o_proj.weight"));
+        qn_w_ = as_f32(tensor_of(tensors, "q_down_norm.weight"), rt.stream);
+        kvn_w_ = as_f32(tensor_of(tensors, "kv_down_norm.weight"), rt.stream);
+        if (sink_) sinks_w_ = as_f32(tensor_of(tensors, "sinks"), rt.stream);
+    }
+    void prepare(Runtime &rt, int max_positions) override { position_->prepare(rt, max_positions); }
+    DeferredNorm forward(Runtime &rt, const Tensor &xn, const DeferredNorm *deferred, const Batch &b, const LayerIO &io, Tensor &residual,
+                         Norm *emit_norm) override {
+        if (io.group < 0 || !io.k_pool || !io.write_cache) fail(FG_E_INTERNAL, "latent_attention: the schedule entry has no cache of its own");
+        const int *table = b.block_tables.at((size_t)io.group);
+        const float *cos_t = position_->cos_table(), *sin_t = position_->sin_table();
+        // [q latent | kv latent and rotated key part | gate], float32: norms and the rotation read them
+        Tensor down = down_.forward(rt, xn, deferred, Tensor(), FG_F32, false, nullptr, nullptr);
+        const int M = (int)down.rows;
+        Tensor cq = rt.arena->matrix(M, qr_, rt.dtype);
+        FG_LAUNCH("mix", fg_rmsnorm_strided, down.ptr<float>(), (int)down.ld, qn_w_.t.ptr<float>(), cq.data, cq.dtype, (int)cq.ld, M, qr_, eps_, rt.stream);
+        Tensor q = q_up_.forward(rt, cq, nullptr, Tensor(), FG_F32, false, nullptr, nullptr);
+        FG_LAUNCH("mix", fg_latent_append, down.ptr<float>() + qr_, (int)down.ld, kvn_w_.t.ptr<float>(), eps_, cos_t, sin_t, dr_ / 2, b.positions,
+                  b.row_seq, table, b.table_width, io.k_pool, io.v_pool, rt.dtype, M, r_, dr_, io.page_size, rt.stream);
+        // per head [q_abs (kv_rank) | q_rot (rot_dim)]
+        Tensor qf = rt.arena->matrix(M, (int64_t)H_ * (r_ + dr_), rt.dtype);
+        FG_LAUNCH("mix", fg_head_gemm, q.data, q.dtype, (int)q.ld, d_ + dr_, k_up_.t.data, k_up_.t.dtype, (int)k_up_.t.ld, 1, qf.data, qf.dtype,
+                  (int)qf.ld, r_ + dr_, nullptr, 0, M, r_, d_, H_, rt.stream);
+        FG_LAUNCH("mix", fg_rope_pairs, q.ptr<float>(), (int)q.ld, d_ + dr_, d_, qf.data, qf.dtype, (int)qf.ld, r_ + dr_, r_, b.positions, cos_t, sin_t,
+                  dr_ / 2, M, H_, dr_, rt.stream);
+        Tensor lat = rt.arena->matrix(M, (int64_t)H_ * r_, rt.dtype);
+        FG_LAUNCH("core", fg_attention_generic_ext, qf.data, (int)qf.ld, lat.data, (int)lat.ld, rt.dtype, b.positions, b.row_seq, table, b.table_width,
+                  io.k_pool, io.v_pool, M, H_, 1, dr_, r_, io.page_size, scale_, 0, 0, 0.f, sink_ ? sinks_w_.t.ptr<float>() : nullptr, 1, rt.stream);
+        Tensor o = rt.arena->matrix(M, (int64_t)H_ * dv_, rt.dtype);
+        const float *gate = gate_ ? down.ptr<float>() + qr_ + r_ + dr_ : nullptr;
+        FG_LAUNCH("mix", fg_head_gemm, lat.data, lat.dtype, (int)lat.ld, r_, v_up_.t.data, v_up_.t.dtype, (int)v_up_.t.ld, 0, o.data, o.dtype, (int)o.ld,
+                  dv_, gate, (int)down.ld, M, dv_, r_, H_, rt.stream);
+        DeferredNorm started;
+        o_.forward(rt, o, nullptr, residual, FG_F32, !rt.overwrite, emit_norm, &started);
+        return started;
+    }
+
+private:
+    int E_ = 0, H_ = 0, d_ = 0, dr_ = 0, dv_ = 0, r_ = 0, qr_ = 0;
+    float scale_ = 1.f, eps_ = 1e-6f;
+    bool sink_ = false, gate_ = false;
+    PositionEncoding *position_ = nullptr;
+    Linear down_, q_up_, o_;
+    Weight k_up_, v_up_, qn_w_, kvn_w_, sinks_w_;
+};
+
+void add_attention_kinds(std::map<std::string, PartFactory> &mixers) {
+    mixers["sink_attention"] = [](Runtime &, const Json &p, BuildContext &c) { return std::make_unique<SinkAttention>(p, c); };
+    mixers["latent_attention"] = [](Runtime &, const Json &p, BuildContext &c) { return std::make_unique<LatentAttention>(p, c); };
+}
+
+}  // namespace fg

@@ -129,7 +129,98 @@ private:
     Weight decay_dev_, ident_cos_, ident_sin_;
 };
 
+// "gated_linear_attention": linear attention whose state decays per key channel by a factor the token itself decides.
+// With the layer's normalised input h, per head (q, k of size head_dim, v of size v_head_dim):
+//     q = W_q h * q_scale, k = W_k h, v = W_v h, g = W_g h       no biases
+//     a = sigmoid(W_a2 (W_a1 h) + b_a2)^(1 / tau)                 a decay per key channel, through a low-rank pair
+//     S_t = diag(a_t) S_(t-1) + k_t v_t^T,  o_t = S_t^T q_t
+//     y = concat_heads(o / sqrt(mean(o^2) + eps) * w_norm) * silu(g),  output W_o y
+// decay_rank (the inner size of the low-rank pair) may be left to the checkpoint's tensor shapes.  q, k, v, g and the
+// low-rank input are ONE contraction with float32 output; the decay logits, their log-sigmoid, the state, the unit norm and
+// the gate stay float32 in every engine dtype (gla.cu), y takes the engine's dtype for the output projection.
+class GatedLinearAttention : public Mixer {
+public:
+    GatedLinearAttention(const Json &p, BuildContext &) {
+        const char *me = "gated_linear_attention";
+        E_ = (int)param_int(p, "hidden_size", me);
+        H_ = (int)param_int(p, "n_heads", me);
+        dk_ = (int)param_int(p, "head_dim", me);
+        dv_ = (int)param_int(p, "v_head_dim", dk_, me);
+        rank_ = (int)param_int(p, "decay_rank", -1, me);
+        eps_ = (float)param_float(p, "eps", me);
+        tau_ = (float)param_float(p, "tau", 1.0, me);
+        q_scale_ = (float)param_float(p, "q_scale", 1.0 / std::sqrt((double)dk_), me);
+        if (E_ <= 0 || H_ <= 0 || dk_ <= 0 || dv_ <= 0 || rank_ == 0 || rank_ < -1) fail(FG_E_CONFIG, "gated_linear_attention: sizes must be positive");
+        if (dv_ > 256) fail(FG_E_CONFIG, format("gated_linear_attention: v_head_dim %d exceeds 256, the largest the kernels take", dv_));
+        if ((size_t)dk_ * dv_ > 40 * 1024) fail(FG_E_CONFIG, "gated_linear_attention: a head's state exceeds what the kernels hold in shared memory");
+        if (!(eps_ > 0.f) || !(tau_ > 0.f)) fail(FG_E_CONFIG, "gated_linear_attention: eps and tau must be positive");
+    }
+    std::vector<TensorDecl> tensor_decls() const override {
+        int64_t Q = (int64_t)H_ * dk_, V = (int64_t)H_ * dv_, R = rank_;
+        return {{"q_proj.weight", {Q, E_}}, {"k_proj.weight", {Q, E_}}, {"v_proj.weight", {V, E_}}, {"g_proj.weight", {V, E_}},
+                {"o_proj.weight", {E_, V}}, {"decay_down.weight", {R, E_}}, {"decay_up.weight", {Q, R}}, {"decay_up.bias", {Q}, false, 0, 1.0f},
+                {"norm.weight", {dv_}, false, 1, 0.01f}};
+    }
+    bool can_overwrite() const override { return true; }
+    bool supports_deferred_norm() const override { return true; }
+    int64_t state_bytes() const override { return (int64_t)H_ * dk_ * dv_ * (int64_t)sizeof(float); }
+    void load(const std::map<std::string, Weight> &tensors, Runtime &rt) override {
+        const Weight &q = tensor_of(tensors, "q_proj.weight"), &k = tensor_of(tensors, "k_proj.weight");
+        const Weight &v = tensor_of(tensors, "v_proj.weight"), &g = tensor_of(tensors, "g_proj.weight");
+        const Weight &a1 = tensor_of(tensors, "decay_down.weight"), &a2 = tensor_of(tensors, "decay_up.weight");
+        if (a1.t.rows != a2.t.cols)
+            fail(FG_E_WEIGHTS, format("gated_linear_attention: the decay's low-rank pair disagrees on its inner size (%lld against %lld)",
+                                      (long long)a1.t.rows, (long long)a2.t.cols));
+        rank_ = (int)a1.t.rows;
+        bool same = q.t.dtype == k.t.dtype && k.t.dtype == v.t.dtype && v.t.dtype == g.t.dtype && g.t.dtype == a1.t.dtype;
+        proj_ = Linear(concat_rows({q, k, v, g, a1}, same ? q.t.dtype : FG_F32, rt.stream));
+        up_ = Linear(a2);
+        o_ = Linear(tensor_of(tensors, "o_proj.weight"));
+        bias_ = concat_rows({tensor_of(tensors, "decay_up.bias")}, FG_F32, rt.stream);
+        norm_ = concat_rows({tensor_of(tensors, "norm.weight")}, FG_F32, rt.stream);
+    }
+    DeferredNorm forward(Runtime &rt, const Tensor &xn, const DeferredNorm *deferred, const Batch &b, const LayerIO &io, Tensor &residual,
+                         Norm *emit_norm) override {
+        if (!io.state || io.state_bytes < state_bytes()) fail(FG_E_INTERNAL, "gated_linear_attention: the schedule entry has no state rows");
+        // what enters the recurrence stays float32: the contraction accumulates in float32 and writes it as it is
+        Tensor proj = proj_.forward(rt, xn, deferred, Tensor(), FG_F32, false, nullptr, nullptr);
+        const int M = (int)proj.rows;
+        const int64_t low_at = (int64_t)2 * H_ * dk_ + (int64_t)2 * H_ * dv_;
+        Tensor low = proj;
+        low.data = proj.ptr<float>() + low_at;
+        low.cols = rank_;
+        Tensor z = up_.forward(rt, low, nullptr, Tensor(), FG_F32, false, nullptr, nullptr);
+        Tensor y = rt.arena->matrix(M, (int64_t)H_ * dv_, rt.dtype);
+        const int *host_cu = b.host_cu_rows.empty() ? nullptr : b.host_cu_rows.data();
+        const int GC = FG_KERNEL("mix", fg_gla_chunk_tokens)();
+        bool chunked = host_cu && !b.single_token && b.max_new >= chunk_threshold_ && FG_KERNEL("mix", fg_gla_chunked_ok)(dk_, dv_);
+        if (chunked) {
+            int n_chunks = 0;
+            for (int s = 0; s < b.n_seq; s++) n_chunks += (host_cu[s + 1] - host_cu[s] + GC - 1) / GC;
+            int *plan = (int *)rt.arena->alloc(((size_t)2 * n_chunks + b.n_seq + 1) * sizeof(int));
+            float *U = (float *)rt.arena->alloc((size_t)n_chunks * H_ * dk_ * dv_ * sizeof(float));
+            float *D = (float *)rt.arena->alloc((size_t)n_chunks * H_ * dk_ * sizeof(float));
+            FG_LAUNCH("mix", fg_gla_chunked, proj.ptr<float>(), (int)proj.ld, z.ptr<float>(), (int)z.ld, bias_.t.ptr<float>(), norm_.t.ptr<float>(),
+                      y.data, y.dtype, (int)y.ld, b.cu_rows, b.slots, (float *)io.state, plan, U, D, b.n_seq, n_chunks, H_, dk_, dv_, tau_,
+                      q_scale_, eps_, rt.stream);
+        } else {
+            FG_LAUNCH("mix", fg_gla, proj.ptr<float>(), (int)proj.ld, z.ptr<float>(), (int)z.ld, bias_.t.ptr<float>(), norm_.t.ptr<float>(), y.data,
+                      y.dtype, (int)y.ld, b.cu_rows, b.slots, (float *)io.state, b.n_seq, H_, dk_, dv_, tau_, q_scale_, eps_, rt.stream);
+        }
+        DeferredNorm started;
+        o_.forward(rt, y, nullptr, residual, FG_F32, !rt.overwrite, emit_norm, &started);
+        return started;
+    }
+
+private:
+    int E_ = 0, H_ = 0, dk_ = 0, dv_ = 0, rank_ = -1, chunk_threshold_ = 32;
+    float eps_ = 0.f, tau_ = 1.f, q_scale_ = 1.f;
+    Linear proj_, up_, o_;
+    Weight bias_, norm_;
+};
+
 void add_recurrent_kinds(std::map<std::string, PartFactory> &mixers) {
+    mixers["gated_linear_attention"] = [](Runtime &, const Json &p, BuildContext &c) { return std::make_unique<GatedLinearAttention>(p, c); };
     mixers["retention"] = [](Runtime &, const Json &p, BuildContext &c) { return std::make_unique<RetentionMixer>(p, c); };
 }
 

@@ -69,6 +69,8 @@ class RunSpec:
     layer: int
     #: index of an EARLIER schedule entry whose cache this run reads instead of owning one
     cache_from: Optional[int] = None
+    #: the model's ``reentry`` map (stream and embedding output -> stream) runs in front of this entry
+    reenter: bool = False
 
 
 @dataclass
@@ -84,13 +86,17 @@ class ModelSpec:
     stop_token_ids: Tuple[int, ...] = ()
     #: regular expressions of checkpoint tensors that may be present without being used
     ignored_tensors: Tuple[str, ...] = ()
+    #: optional map of the residual stream that also reads the embedding's output (schedule entries ask for it)
+    reentry: Optional[PartSpec] = None
 
     def to_json(self) -> dict:
+        extra = {"reentry": self.reentry.to_json()} if self.reentry is not None else {}
         return {
+            **extra,
             "hidden_size": self.hidden_size, "vocab_size": self.vocab_size, "max_positions": self.max_positions,
             "embedding": self.embedding.to_json(), "final_norm": self.final_norm.to_json(), "head": self.head.to_json(),
             "layers": [l.to_json() for l in self.layers],
-            "schedule": [{"layer": r.layer, "cache_from": r.cache_from} for r in self.schedule],
+            "schedule": [{"layer": r.layer, "cache_from": r.cache_from, "reenter": r.reenter} for r in self.schedule],
             "stop_token_ids": list(self.stop_token_ids), "ignored_tensors": list(self.ignored_tensors),
         }
 
@@ -105,6 +111,7 @@ class ModelSpec:
             embedding=P(j["embedding"]), final_norm=P(j["final_norm"]), head=P(j["head"]),
             layers=[LayerSpec(l["block"], P(l["mixer"]), O(l.get("feed_forward")), P(l["mixer_norm"]), O(l.get("feed_forward_norm")),
                               O(l.get("mixer_post_norm")), O(l.get("feed_forward_post_norm"))) for l in j["layers"]],
-            schedule=[RunSpec(r["layer"], r.get("cache_from")) for r in j["schedule"]],
+            schedule=[RunSpec(r["layer"], r.get("cache_from"), bool(r.get("reenter", False))) for r in j["schedule"]],
+            reentry=O(j.get("reentry")),
             stop_token_ids=tuple(j.get("stop_token_ids") or ()), ignored_tensors=tuple(j.get("ignored_tensors") or ()),
         )

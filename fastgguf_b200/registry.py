@@ -17,9 +17,10 @@ from . import capi
 from .config.base import ModelConfig
 from .config.llama import LlamaConfig
 from .config.zirivik import ZirivikConfig
+from .config.salulorn import SalulornConfig
 from .engine.spec import ModelSpec
 
-_CLASSES = {"LlamaForCausalLM": LlamaConfig, "Zirivik": ZirivikConfig}
+_CLASSES = {"LlamaForCausalLM": LlamaConfig, "Zirivik": ZirivikConfig, "Salulorn": SalulornConfig}
 _keep_alive = []
 
 
