@@ -3,7 +3,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--model 1b|3b|8b] [--dtype bfloat16|float32]
                     [--layers L] [--no-points] [--no-prefill] [--impl reference]
-    python bench.py --compare zirivik [--sizes s,m] [--steps K] [--warmup W] [--batch 8]
+    python bench.py --compare zirivik|salulorn [--sizes s,m] [--steps K] [--warmup W] [--batch 8]
 
 Default run: the layer sizes of Llama 3.2 1B with random weights, bfloat16, a batch of 8 sequences with random
 prompts of unequal lengths 128..1024, context 4096.  ``--model 3b``: prompts 64..2048, context 4096; ``--model 8b``:
@@ -15,8 +15,8 @@ read (every weight once, the cache of the live requests) by its time; ``points``
 at the headline batch with the reference's default sampler instead of greedy; ``points_detail`` what each of them was
 made of.  Every step reads gigabytes of weights, far more than the 126 MB L2, so no flush is needed between timed steps.
 
-``--compare zirivik`` leaves all of that alone and prints another line: prefill (one step of 2,048 tokens) and decode
-(graph-replayed steps of a batch) of Zirivik models whose layers have the sizes of real models, beside Llama models
+``--compare zirivik`` (or ``salulorn``) leaves all of that alone and prints another line: prefill (one step of 2,048 tokens)
+and decode (graph-replayed steps of a batch) of models of that design whose layers have the sizes of real models, beside Llama models
 of the same width, depth, heads and feed-forward size, with the device time of every launcher of one prefill step and
 of decode steps run eagerly (``profile``), so that like kernels can be set side by side.
 """
@@ -148,11 +148,33 @@ def zirivik_config(width, heads, kv_heads, head_dim, ff, vocab, window, expert_f
             "logit_softcap": 30.0, "layers": layers}
 
 
+def salulorn_config(width, heads, kv_heads, head_dim, ff, vocab, window, expert_ff, blocks=2):
+    """Layers of a real model's sizes in the design's own mix: gated linear attention, windowed attention with a short
+    convolution, gated linear attention, latent attention, each beside a dense feed-forward; `blocks` times; the whole
+    stack is a loop that runs once, so the loop's input map is part of the step."""
+    del expert_ff
+    g = {"heads": width // 128, "dim": 64, "vdim": 128, "tau": 16.0, "decay_rank": 16}
+    att = {"heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim, "scale": head_dim ** -0.5, "conv": 4,
+           "mask": {"size": window}, "rot": {"base": 1000000.0, "dims": head_dim}, "softcap": 50.0}
+    lat = {"heads": heads, "dim": head_dim, "rot_dim": 64, "vdim": head_dim, "kv_rank": 512, "q_rank": width * 3 // 4,
+           "scale": (head_dim + 64) ** -0.5,
+           "rot": {"base": 10000.0, "dims": 64, "scaling": {"factor": 40.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    dense = {"kind": "dense", "ff": ff}
+    layers = []
+    for _ in range(blocks):
+        layers += [{"type": "gla", "mixer": g, "mlp": dense}, {"type": "attention", "mixer": att, "mlp": dense},
+                   {"type": "gla", "mixer": g, "mlp": dense}, {"type": "latent_attention", "mixer": lat, "mlp": dense}]
+    return {"architecture": "Salulorn", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "layers": layers,
+            "loop": {"start": 0, "stop": len(layers), "times": 1}}
+
+
+DESIGNS = {"zirivik": zirivik_config, "salulorn": salulorn_config}
+
 #: name -> (width, heads, kv_heads, head_dim, ff, vocab, window, expert_ff)
 COMPARE_SIZES = {"s": (2048, 32, 8, 64, 8192, 32768, 1024, 2048), "m": (4096, 32, 8, 128, 14336, 32768, 2048, 4096)}
 
 
-def compare_zirivik(args):
+def compare_designs(args):
     import numpy as np
     import torch
     from fastgguf_b200.engine.api import Engine
@@ -161,15 +183,16 @@ def compare_zirivik(args):
     from fastgguf_b200.sampling import SamplingParams
     W, K, B = max(3, args.warmup), args.steps, args.batch
     rng = np.random.default_rng(0)
-    out = {"compare": "zirivik", "dtype": args.dtype, "batch": B, "prefill_tokens": PREFILL_TOKENS, "steps": K, "warmup": W,
+    design = args.compare
+    out = {"compare": design, "dtype": args.dtype, "batch": B, "prefill_tokens": PREFILL_TOKENS, "steps": K, "warmup": W,
            "peaks": peaks(), "sizes": {}}
     for name in args.sizes.split(","):
         width, heads, kv, hd, ff, vocab, window, eff = COMPARE_SIZES[name]
-        z = zirivik_config(width, heads, kv, hd, ff, vocab, window, eff)
+        z = DESIGNS[design](width, heads, kv, hd, ff, vocab, window, eff)
         llama = dict(LLAMA_3_2_1B, hidden_size=width, num_hidden_layers=len(z["layers"]), num_attention_heads=heads,
                      num_key_value_heads=kv, head_dim=hd, intermediate_size=ff, vocab_size=vocab, rope_scaling=None, bos_token_id=1, eos_token_id=2)
         row = {}
-        for label, cd in (("zirivik", z), ("llama", llama)):
+        for label, cd in ((design, z), ("llama", llama)):
             cfg = config_from_dict(cd)
             per_seq = (1024 + W + K * 3 + 128 + 63) // 64 * 64
             engine = Engine.from_random(cfg, 0, dtype=args.dtype, max_tokens=max(B * per_seq, PREFILL_TOKENS + 64) + 64 * B,
@@ -223,8 +246,12 @@ def compare_zirivik(args):
                           "profile_prompt_and_8_decode_steps": [{"name": r["name"], "calls": r["calls"], "ms": round(r["ms"], 4)}
                                                                for r in prof_all]}
             del engine
-        row["config"] = {"width": width, "heads": heads, "kv_heads": kv, "head_dim": hd, "ff": ff, "vocab": vocab, "window": window,
-                         "experts": "8 of ff %d, 2 a row" % eff, "retention": "%d heads of 128 x 128" % (width // 128)}
+        row["config"] = {"width": width, "heads": heads, "kv_heads": kv, "head_dim": hd, "ff": ff, "vocab": vocab, "window": window}
+        if design == "zirivik":
+            row["config"].update({"experts": "8 of ff %d, 2 a row" % eff, "retention": "%d heads of 128 x 128" % (width // 128)})
+        else:
+            row["config"].update({"gla": "%d heads of 64 x 128" % (width // 128), "latent": "rank 512 + 64 rotated, queries through %d" % (width * 3 // 4),
+                                  "convolution": "4 taps", "loop": "all layers, once"})
         out["sizes"][name] = row
     return out
 
@@ -254,7 +281,7 @@ def main():
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points")
     ap.add_argument("--no-prefill", action="store_true", help="skip the prefill measurement")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end measurement")
-    ap.add_argument("--compare", default=None, choices=["zirivik"],
+    ap.add_argument("--compare", default=None, choices=sorted(DESIGNS),
                     help="another line instead of the default one: this design beside Llama at equal sizes, prefill and decode")
     ap.add_argument("--sizes", default="s", help="with --compare: which sizes, of " + ",".join(sorted(COMPARE_SIZES)))
     args = ap.parse_args()
@@ -271,7 +298,7 @@ def main():
             return 2
         if args.steps == 256:
             args.steps = 64
-        print(json.dumps(compare_zirivik(args)))
+        print(json.dumps(compare_designs(args)))
         return 0
 
     import numpy as np

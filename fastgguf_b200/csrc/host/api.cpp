@@ -182,6 +182,8 @@ int fg_write_random_model(const fg_config *cfg, uint64_t seed, const char *out_d
             t.name = kv.first;
             t.dtype = kv.second.is_int ? FG_I32 : dtype;
             t.shape = kv.second.shape;
+            for (int64_t n : t.shape)
+                if (n < 0) fail(FG_E_CONFIG, "tensor '" + kv.first + "' has a size that only a checkpoint can give; random weights need it in the configuration");
             tensors.push_back(std::move(t));
         }
         Json meta = Json::object();

@@ -331,7 +331,7 @@ Json SalulornConfig::spec() const {
         Json r = Json::object();
         r.set("layer", run.first);
         r.set("cache_from", Json());
-        r.set("reenter", run.second);
+        if (run.second) r.set("reenter", true);
         schedule.push(r);
     }
     Json ep = Json::object(), hp = Json::object(), et = Json::object(), ht = Json::object();

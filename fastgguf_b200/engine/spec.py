@@ -96,7 +96,7 @@ class ModelSpec:
             "hidden_size": self.hidden_size, "vocab_size": self.vocab_size, "max_positions": self.max_positions,
             "embedding": self.embedding.to_json(), "final_norm": self.final_norm.to_json(), "head": self.head.to_json(),
             "layers": [l.to_json() for l in self.layers],
-            "schedule": [{"layer": r.layer, "cache_from": r.cache_from, "reenter": r.reenter} for r in self.schedule],
+            "schedule": [dict({"layer": r.layer, "cache_from": r.cache_from}, **({"reenter": True} if r.reenter else {})) for r in self.schedule],
             "stop_token_ids": list(self.stop_token_ids), "ignored_tensors": list(self.ignored_tensors),
         }
 

@@ -1,0 +1,407 @@
+"""The Salulorn decoder in the engine against the plain implementation (``plain_salulorn``): each mechanism alone, whole
+prompts, portions, decoding, batches, reused slots and pages, and generation through the entry point.
+
+Structure is tested in float32, where any key wrongly seen or missed, any state lost or kept too long is orders of
+magnitude above the tolerance; the bfloat16 runs use sharpened attention (see ``salulorn_cases.random_weights``) so that
+the same faults stay visible above rounding."""
+import numpy as np
+import pytest
+import torch
+
+import plain_salulorn as ps
+from helpers import rel_err
+from salulorn_cases import CASES, attention, config, dense, gla, latent, make_model
+
+pytestmark = pytest.mark.gpu
+
+#: max |dlogit| / max |logit| against the float64 plain implementation; a key wrongly seen or a lost state is at 1e-3 and above
+TOL = {"float32": 2e-5, "bfloat16": 6e-2}
+
+
+def tokens_for(case, n, seed):
+    rng = np.random.default_rng(seed)
+    return [int(t) for t in rng.integers(0, case[0]["vocab"], size=n)]
+
+
+def engine_for(model_dir, dtype, **kw):
+    from fastgguf_b200.engine.api import Engine
+    args = dict(dtype=dtype, max_tokens=4096, max_batch=8)
+    args.update(kw)
+    return Engine.from_dir(model_dir, **args)
+
+
+def entry(slot, toks, want=None):
+    from fastgguf_b200.engine.batch import StepEntry
+    return StepEntry(slot, toks, list(range(len(toks))) if want is None else want)
+
+
+def early(p):
+    """A sequence's first tokens pass q . k (a sum that may nearly cancel) through the recurrent mixer's unit norm, which
+    removes its size and keeps its rounding, and the two forms of that mixer's kernel add in different orders: five times
+    the tolerance there, still far below a structural fault."""
+    return 5 if p < 4 else 1
+
+
+def plain_logits(case, W, toks):
+    return ps.forward(case[0], W, toks)[0].numpy()
+
+
+@pytest.fixture(scope="module")
+def models(tmp_path_factory):
+    """(case, 1.0): the case as it is; (case, 3.0): attention sharpened, for bfloat16."""
+    out = {}
+    for i, (name, case) in enumerate(CASES.items()):
+        for sharp in (1.0, 3.0):
+            d, W = make_model(tmp_path_factory.mktemp(f"s_{name}_{int(sharp)}"), case, 100 + i, sharp)
+            out[(name, sharp)] = (d, case, W)
+    return out
+
+
+# ------------------------------------------------------------------------------ mechanisms alone
+@pytest.mark.parametrize("scaling", [None, (8.0, 256, 16.0, 2.0), (40.0, 64, 32.0, 1.0)])
+def test_rotary_tables_with_and_without_scaling(scaling):
+    """The tables the rotation kernels read: pair i of a position holds amplitude * cos / sin of position * frequency."""
+    from fastgguf_b200.parts import position_tables
+    rot = {"base": 5000.0, "dims": 24}
+    params = {"head_dim": 32, "theta": 5000.0, "rotary_dim": 24, "layout": "adjacent", "scaling": None}
+    if scaling:
+        rot["scaling"] = dict(zip(("factor", "original", "fast", "slow"), scaling))
+        params["scaling"] = {"rope_type": "yarn", "factor": scaling[0], "original_max_position_embeddings": scaling[1],
+                             "beta_fast": scaling[2], "beta_slow": scaling[3]}
+    cos, sin, _ = position_tables("rope", params, 300)
+    f, amp = ps.rotary_frequencies(rot)
+    ang = torch.arange(300, dtype=torch.float64)[:, None] * f[None, :]
+    assert np.abs(cos[:, :12] - (torch.cos(ang) * amp).numpy()).max() < 2e-6
+    assert np.abs(sin[:, :12] - (torch.sin(ang) * amp).numpy()).max() < 2e-6
+    assert np.all(cos[:, 12:] == 1.0) and np.all(sin[:, 12:] == 0.0)       # dimensions that are not rotated
+    if scaling:
+        assert abs(amp - 1.0) > 0.05 and not torch.allclose(f, ps.rotary_frequencies({"base": 5000.0, "dims": 24})[0])
+
+
+def one_layer(layer, mlp=None, width=80, vocab=50):
+    return config(width, vocab, [(layer, mlp)])
+
+
+MIXERS = {
+    "gla, small": gla(3, 16, 24, 4.0, 5),
+    "gla, fast decays, one head": gla(1, 64, 16, 0.5, 3),
+    "gla, value size that does not divide the block": gla(2, 16, 48, 16.0, 7),
+    "attention, all keys, nothing else": attention(4, 2, 24, 40, 0.3),
+    "attention, window": attention(6, 1, 16, 16, 0.4, size=5),
+    "attention, window of one, convolution of two taps": attention(2, 2, 16, 16, 0.5, conv=2, size=1),
+    "attention, convolution, cap, some dimensions rotated": attention(3, 3, 32, 8, 0.2, conv=4, rot=(100.0, 12), softcap=2.0),
+    "attention, one tap": attention(2, 1, 24, 24, 0.2, conv=1, size=11, rot=(10000.0, 24)),
+    "latent attention, small": latent(3, 16, 8, 24, 40, 48, 0.2, 10000.0),
+    "latent attention, scaled frequencies, one head": latent(1, 8, 16, 8, 12, 20, 0.3, 500.0, scaling=(6.0, 32, 8.0, 1.0)),
+    "long gla, head 128": gla(2, 128, 128, 16.0, 16),
+    "long gla, keys 64 and values 128": gla(2, 64, 128, 2.0, 8),
+    "long attention, window past a page, head 64": attention(4, 2, 64, 64, 0.125, conv=3, size=70, rot=(250000.0, 64), softcap=30.0),
+    "long attention, window of a page, keys 128 and values 64": attention(2, 1, 128, 64, 0.09, size=64, rot=(1000.0, 32)),
+    "long latent attention, wide latent": latent(4, 64, 32, 64, 160, 96, 0.1, 10000.0, scaling=(16.0, 128, 32.0, 1.0)),
+}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", list(MIXERS))
+def test_mixer_alone(tmp_path, name, dtype):
+    """One layer of a mixer alone (norm, mixer, residual add) on rows given by the test: a portion of 37 rows, then one of
+    2, then single rows, so the second and later calls start from what the first left behind (the long cases: 160, 30 and
+    2 rows, then 38 single ones)."""
+    case = one_layer(MIXERS[name])
+    d, W = make_model(tmp_path, case, 7, sharp=2.0)
+    eng = engine_for(d, dtype)
+    g = torch.Generator().manual_seed(8)
+    cuts = [160, 30, 2] + [1] * 38 if name.startswith("long") else [37, 2, 1, 1, 1, 1, 1, 1]
+    T = sum(cuts)
+    x = torch.randn(T, case[0]["width"], generator=g, dtype=torch.float64)
+    layer = case[0]["layers"][0]
+    h = ps.rms_norm(x, W["l0.norm1"], 1e-5)
+    want = (x + ps.MIXERS[layer["type"]](h, W, "l0.mix.", layer["mixer"], 1e-5)).numpy()
+    slot = eng.acquire()
+    got, at = [], 0
+    for n in cuts:
+        part = np.ascontiguousarray(x[at:at + n].numpy(), dtype=np.float32)
+        got.append(eng.block_forward(0, [(slot, n)], part))
+        at += n
+    got = np.concatenate(got)
+    tol = 1e-5 if dtype == "float32" else 4e-2
+    for r in range(T):
+        assert rel_err(got[r], want[r]) < tol, (name, r)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_parallel_block_adds_both_sublayers(tmp_path, dtype):
+    """norm once, mixer and feed-forward both on its output, both added to the stream."""
+    case = one_layer(attention(2, 1, 16, 16, 0.25, size=6), dense(56))
+    d, W = make_model(tmp_path, case, 9)
+    eng = engine_for(d, dtype)
+    x = torch.randn(20, 80, generator=torch.Generator().manual_seed(1), dtype=torch.float64)
+    h = ps.rms_norm(x, W["l0.norm1"], 1e-5)
+    mixer = ps.attention_mixer(h, W, "l0.mix.", case[0]["layers"][0]["mixer"], 1e-5)
+    want = x + mixer + ps.dense_ff(h, W, "l0.mlp.")
+    got = eng.block_forward(0, [(eng.acquire(), 20)], np.ascontiguousarray(x.numpy(), dtype=np.float32))
+    assert rel_err(got, want.numpy()) < (1e-5 if dtype == "float32" else 3e-2)
+    assert rel_err(got, (x + mixer).numpy()) > 1e-2            # the feed-forward is there
+
+
+def test_sink_takes_weight_from_the_keys(tmp_path):
+    """Large sinks shrink what attention returns; the engine follows the plain implementation, and both differ by far
+    from attention without a sink."""
+    for layer in (attention(3, 1, 16, 24, 0.3), latent(3, 16, 8, 24, 20, 24, 0.25, 1000.0)):
+        case = one_layer(layer)
+        d, W = make_model(tmp_path / layer["type"], case, 10, sink=4.0)
+        eng = engine_for(d, "float32")
+        x = torch.randn(30, 80, generator=torch.Generator().manual_seed(2), dtype=torch.float64)
+        h = ps.rms_norm(x, W["l0.norm1"], 1e-5)
+        f = ps.MIXERS[layer["type"]]
+        want = x + f(h, W, "l0.mix.", layer["mixer"], 1e-5)
+        none = x + f(h, {k: v for k, v in W.items() if not k.endswith("sink")}, "l0.mix.", layer["mixer"], 1e-5)
+        got = eng.block_forward(0, [(eng.acquire(), 30)], np.ascontiguousarray(x.numpy(), dtype=np.float32))
+        assert rel_err(got, want.numpy()) < 1e-5
+        assert rel_err(none.numpy(), want.numpy()) > 1e-2
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("size", [7, 64, 65])
+def test_one_key_at_the_windows_edge(tmp_path, size, dtype):
+    """Weights and inputs made so that ONE key far outweighs all others for every later query: the key projection is the
+    query projection with its input columns shifted, the special row is the later rows' common direction shifted back.
+    The last row that still sees that key returns its value, the next row does not - in a prompt and decoded one by one."""
+    from salulorn_cases import random_weights, write_model
+    layer = attention(2, 1, 16, 16, 1.0, size=size)
+    case = one_layer(layer)
+    E, special = 80, 20
+    T = special + size + 20
+    W = random_weights(case, 11)
+    W["l0.mix.q"] = W["l0.mix.q"][:16].repeat(2, 1)                 # both query heads ask the one key head the same
+    W["l0.mix.k"] = torch.roll(W["l0.mix.q"][:16], 1, dims=1)      # k(h) = q(h shifted back by one column)
+    for k in ("l0.mix.q.b", "l0.mix.k.b"):
+        W[k] = torch.zeros_like(W[k])
+    for k in ("l0.norm1", "l0.mix.q.norm", "l0.mix.k.norm"):
+        W[k] = torch.ones_like(W[k])
+    W["l0.mix.sink"] = torch.full_like(W["l0.mix.sink"], -20.0)
+    d = write_model(tmp_path, case, W)
+    W = {k: v.double() for k, v in W.items()}
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(T, E, generator=g, dtype=torch.float64)
+    w = torch.randn(E, generator=g, dtype=torch.float64)
+    x[special] = torch.roll(w, 1)                                   # its key is the query of direction w
+    x[special + 1:] = w[None, :] + 0.05 * x[special + 1:]
+    want = (x + ps.attention_mixer(ps.rms_norm(x, W["l0.norm1"], 1e-5), W, "l0.mix.", layer["mixer"], 1e-5)).numpy()
+    last_in, first_out = special + size - 1, special + size
+    mixed = want - x.numpy()
+    assert np.abs(mixed[last_in] - mixed[first_out]).max() > 0.3 * np.abs(mixed[last_in]).max()      # the edge shows
+    tol = 1e-5 if dtype == "float32" else 4e-2
+    for cuts in ([T], [last_in - 3] + [1] * (T - last_in + 3)):
+        eng = engine_for(d, dtype)
+        slot, at, got = eng.acquire(), 0, []
+        for n in cuts:
+            got.append(eng.block_forward(0, [(slot, n)], np.ascontiguousarray(x[at:at + n].numpy(), dtype=np.float32)))
+            at += n
+        got = np.concatenate(got)
+        for r in (special, special + 1, last_in - 1, last_in, first_out, first_out + 1, T - 1):
+            assert rel_err(got[r], want[r]) < tol, (size, cuts[0], r)
+
+
+# ------------------------------------------------------------------------------ whole models
+@pytest.mark.parametrize("dtype,sharp", [("float32", 1.0), ("bfloat16", 3.0)])
+@pytest.mark.parametrize("which", list(CASES))
+def test_whole_prompt(models, which, dtype, sharp):
+    """Logits at every position of a prompt that passes every window and page edge of the case."""
+    d, case, W = models[(which, sharp)]
+    toks = tokens_for(case, 150, 11)
+    want = plain_logits(case, W, toks)
+    eng = engine_for(d, dtype)
+    s = eng.acquire()
+    got = eng.step_host([entry(s, toks)])
+    for p in range(len(toks)):
+        assert rel_err(got[p], want[p]) < TOL[dtype], (which, p)
+    eng.release(s)
+    eng.cache.check()
+
+
+def test_the_first_tokens(models):
+    """Sequences of one, two and three tokens, as a prompt and one by one: convolutions and windows that reach in front
+    of the sequence's start see zeros and nothing."""
+    for which in CASES:
+        d, case, W = models[(which, 1.0)]
+        eng = engine_for(d, "float32")
+        for n in (1, 2, 3, 5):
+            toks = tokens_for(case, n, 30 + n)
+            want = plain_logits(case, W, toks)
+            s = eng.acquire()
+            assert rel_err(eng.step_host([entry(s, toks)]), want) < TOL["float32"], (which, n)
+            eng.release(s)
+            s = eng.acquire()
+            got = np.concatenate([eng.step_host([entry(s, [t])]) for t in toks])
+            assert rel_err(got, want) < TOL["float32"], (which, n)
+            eng.release(s)
+
+
+@pytest.mark.parametrize("dtype,sharp", [("float32", 1.0), ("bfloat16", 3.0)])
+@pytest.mark.parametrize("which,cuts", [("a", [2, 2, 3, 17, 33, 64, 65, 2, 31]), ("b", [63, 2, 64, 1, 1, 70, 2, 16]),
+                                        ("c", [100, 28, 1, 2, 64, 24]), ("d", [3, 2, 40, 2])])
+def test_portions_and_decoding(models, which, cuts, dtype, sharp):
+    """A prompt cut into portions of many sizes, down to two tokens and one, then 40 tokens one by one: the same logits
+    as the whole sequence at every position."""
+    d, case, W = models[(which, sharp)]
+    n = sum(cuts) + 40
+    toks = tokens_for(case, n, 13)
+    want = plain_logits(case, W, toks)
+    eng = engine_for(d, dtype)
+    s = eng.acquire()
+    at = 0
+    for c in cuts + [1] * 40:
+        got = eng.step_host([entry(s, toks[at:at + c])])
+        for i in range(c):
+            assert rel_err(got[i], want[at + i]) < TOL[dtype], (which, at + i, c)
+        at += c
+    eng.release(s)
+    eng.cache.check()
+
+
+@pytest.mark.parametrize("dtype,sharp", [("float32", 1.0), ("bfloat16", 3.0)])
+@pytest.mark.parametrize("which", list(CASES))
+def test_batch_of_unequal_requests(models, which, dtype, sharp):
+    """Five requests of 1 to 140 tokens in one step, then decoded together while the shorter ones leave: every
+    request's logits equal those it has alone."""
+    d, case, W = models[(which, sharp)]
+    lens, total = [1, 140, 64, 7, 65], [9, 150, 70, 30, 66]
+    toks = [tokens_for(case, t, 20 + i) for i, t in enumerate(total)]
+    want = [plain_logits(case, W, t) for t in toks]
+    eng = engine_for(d, dtype)
+    slots = [eng.acquire() for _ in toks]
+    got = eng.step_host([entry(s, t[:n]) for s, t, n in zip(slots, toks, lens)])
+    row = 0
+    for b, n in enumerate(lens):
+        for p in range(n):
+            assert rel_err(got[row], want[b][p]) < TOL[dtype] * early(p), (which, b, p)
+            row += 1
+    at = list(lens)
+    alive = list(range(len(toks)))
+    while alive:
+        got = eng.step_host([entry(slots[b], [toks[b][at[b]]]) for b in alive])
+        for i, b in enumerate(alive):
+            assert rel_err(got[i], want[b][at[b]]) < TOL[dtype] * early(at[b]), (which, b, at[b])
+            at[b] += 1
+        for b in [b for b in alive if at[b] == total[b]]:
+            eng.release(slots[b])
+            alive.remove(b)
+    eng.cache.check()
+    assert eng.cache.live_slots() == []
+
+
+def test_slots_and_pages_used_again(models):
+    """Sequences come and go in a cache of two slots and few pages: a new sequence starts from nothing (state rows - the
+    recurrence's and the convolution's - are cleared, pages of the one before are not read), also after a sequence that
+    was released halfway."""
+    d, case, W = models[("b", 1.0)]
+    eng = engine_for(d, "float32", max_tokens=512, max_batch=2)
+    seqs = [tokens_for(case, n, 40 + i) for i, n in enumerate([200, 130, 90, 260, 70, 140])]
+    for k, toks in enumerate(seqs):
+        s = eng.acquire()
+        other = eng.acquire()
+        eng.step_host([entry(other, seqs[(k + 1) % len(seqs)][:50], [])])       # a neighbour that is dropped halfway
+        want = plain_logits(case, W, toks)
+        head = len(toks) - 20
+        got = eng.step_host([entry(s, toks[:head], [head - 1])])
+        assert rel_err(got[0], want[head - 1]) < TOL["float32"], k
+        eng.release(other)
+        for p in range(head, len(toks)):
+            got = eng.step_host([entry(s, [toks[p]])])
+            assert rel_err(got[0], want[p]) < TOL["float32"], (k, p)
+        eng.release(s)
+        eng.cache.check()
+
+
+def test_long_decoding_past_windows_and_pages(models):
+    """300 tokens one by one after a short prompt: windows slide over decoded tokens, pages leave the windowed groups, and
+    the recurrent state carries the first tokens all along."""
+    d, case, W = models[("b", 1.0)]
+    toks = tokens_for(case, 330, 50)
+    want = plain_logits(case, W, toks)
+    eng = engine_for(d, "float32")
+    s = eng.acquire()
+    eng.step_host([entry(s, toks[:30], [])])
+    for p in range(30, 330):
+        got = eng.step_host([entry(s, [toks[p]])])
+        assert rel_err(got[0], want[p]) < TOL["float32"], p
+    assert any(g["window"] for g in eng.cache.groups) and any(not g["window"] for g in eng.cache.groups)
+    eng.release(s)
+    eng.cache.check()
+
+
+def test_a_far_token_is_remembered(tmp_path):
+    """One early token differs between two prompts of 400 tokens: through the slowly decaying state, and through latent
+    attention over all keys, the last logits differ by far more than rounding, in the engine exactly as in the plain
+    implementation; with the window alone they would not."""
+    for far in (gla(2, 16, 16, 64.0, 4), latent(2, 16, 8, 16, 24, 24, 0.4, 10000.0)):
+        case = config(64, 90, [(far, dense(48)), (attention(2, 1, 16, 16, 0.25, conv=2, size=8), None)])
+        d, W = make_model(tmp_path / far["type"], case, 60, sharp=2.0)
+        a = tokens_for(case, 400, 61)
+        b = list(a)
+        b[3] = (a[3] + 1) % case[0]["vocab"]
+        eng = engine_for(d, "float32")
+        last = []
+        for toks in (a, b):
+            s = eng.acquire()
+            got = eng.step_host([entry(s, toks[:380], [])])
+            for p in range(380, 400):
+                got = eng.step_host([entry(s, [toks[p]])])
+            last.append(got[0])
+            eng.release(s)
+            assert rel_err(got[0], plain_logits(case, W, toks)[-1]) < TOL["float32"]
+        assert np.abs(last[0] - last[1]).max() > 1e-3 * np.abs(last[0]).max(), far["type"]
+
+
+# ------------------------------------------------------------------------------ generation through the entry point
+@pytest.mark.parametrize("use_graphs", [False, True])
+@pytest.mark.parametrize("which", ["a", "b"])
+def test_greedy_generation(models, which, use_graphs):
+    """Greedy decoding through Engine.generate - the scheduler's batches, the recorded decode step, slots that come
+    back - follows the plain implementation: each token is the plain logits' best given the tokens before it (where the
+    best two are closer than rounding, either counts)."""
+    d, case, W = models[(which, 1.0)]
+    prompts = [tokens_for(case, n, 70 + i) for i, n in enumerate([5, 70, 1, 33, 12])]
+    eng = engine_for(d, "float32", max_tokens=2048, max_batch=4, use_graphs=use_graphs)
+    out = eng.generate(prompts, temp=0, max_tokens=24, ignore_eos=True, batch_size=3)
+    for p, c in zip(prompts, out):
+        assert len(c.tokens) == 24
+        logits = plain_logits(case, W, p + c.tokens)
+        for i, t in enumerate(c.tokens):
+            row = logits[len(p) + i - 1]
+            assert row[t] >= row.max() - 1e-4 * np.abs(row).max(), (which, i)
+    eng.cache.check()
+    assert eng.cache.live_slots() == []
+
+
+def test_generation_in_bfloat16_runs_the_recorded_step(models):
+    d, case, W = models[("c", 1.0)]
+    prompts = [tokens_for(case, n, 80 + i) for i, n in enumerate([9, 40])]
+    eng = engine_for(d, "bfloat16", max_tokens=1024, max_batch=2)
+    out = eng.generate(prompts, temp=0, max_tokens=70, ignore_eos=True)
+    for p, c in zip(prompts, out):
+        logits = plain_logits(case, W, p + c.tokens)
+        close = sum(logits[len(p) + i - 1][t] >= logits[len(p) + i - 1].max() - 0.05 * np.abs(logits[len(p) + i - 1]).max()
+                    for i, t in enumerate(c.tokens))
+        assert close >= 0.9 * len(c.tokens)
+    eng.cache.check()
+
+
+def test_command_line_generates(models):
+    """``python -m fastgguf_b200 generate`` on a Salulorn folder: the model class comes from config.json, the tokens are
+    those of Engine.generate."""
+    import json
+    import os
+    import subprocess
+    import sys
+    d, case, W = models[("a", 1.0)]
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    p = subprocess.run([sys.executable, "-m", "fastgguf_b200", "generate", d, "256", "--prompt", "5,17,3,200", "--prompt", "9",
+                        "--temp", "0", "--max-tokens", "6", "--ignore-eos", "--dtype", "float32", "--json"],
+                       cwd=root, capture_output=True, text=True)
+    assert p.returncode == 0, p.stderr
+    got = [r["tokens"] for r in json.loads(p.stdout)]
+    eng = engine_for(d, "float32", max_tokens=512, max_batch=2)
+    want = [c.tokens for c in eng.generate([[5, 17, 3, 200], [9]], temp=0, max_tokens=6, ignore_eos=True)]
+    assert got == want
