@@ -261,6 +261,12 @@ def kernel_modules_for(spec_json, dtype_code: int) -> tuple:
             if role == "mixer" and part.get("kind") == "gqa_attention" and p.get("head_dim") in (64, 128) \
                     and p.get("v_head_dim", p.get("head_dim")) == p.get("head_dim"):
                 fast_attention = True
+            if role == "mixer" and part.get("kind") == "sink_attention" and p.get("head_dim") in (64, 128) \
+                    and p.get("v_head_dim", p.get("head_dim")) == p.get("head_dim"):
+                fast_attention = True
+            if role == "mixer" and part.get("kind") == "latent_attention" and p.get("head_dim", 0) + p.get("rot_dim", 0) in (64, 128) \
+                    and p.get("v_head_dim", 0) <= p.get("head_dim", 0) + p.get("rot_dim", 0):
+                fast_attention = True
     builtin = {"gqa_attention", "swiglu", "retention", "mlp", "moe", "gated_linear_attention", "sink_attention", "latent_attention", None}
     if dtype_code == FG_BF16 and (fast_attention or kinds - builtin):
         modules.append("attn")

@@ -43,6 +43,8 @@ struct RopeArgs {
     bf16 *k_pool, *v_pool;           // the cache, writable
     int q_heads;                     // H: k starts at q + H * HD, v at q + (H + KV) * HD
     int keep_first;                  // with a window: the sequence's first keys stay visible (both forms of the kernel)
+    float softcap;                   // > 0: capped scores (both forms)
+    const float *sinks;              // or null: a float per query head that joins the softmax's denominator once
 };
 
 template <int HD, bool CLUSTER, bool FUSE>
@@ -88,6 +90,16 @@ attn_decode_kernel(const bf16 *__restrict__ q, int ldq, const int *__restrict__ 
     for (int d = 0; d < HD / 8; d++) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
     const int lo[2] = {lo_key, lo_key}, hi[2] = {pos, pos};
+    if (rope.sinks && split == 0 && warp == 0) {
+        // the sink counts once a row: in the first warp of the first split, which always has a page (its results are merged
+        // with the other warps' and splits' like any other partial softmax)
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            const int r = (lane >> 2) + 8 * i;
+            if (r < rows) { m[i] = rope.sinks[kvh * G + g0 + r] * LOG2E; l[i] = 1.f; }
+        }
+    }
+    const float cap_log2 = rope.softcap > 0.f ? rope.softcap * LOG2E : 0.f, cap_in = rope.softcap > 0.f ? scale / rope.softcap : 0.f;
 
     int p = p_begin + warp;
     if (p < p_end) {
@@ -182,9 +194,9 @@ attn_decode_kernel(const bf16 *__restrict__ q, int ldq, const int *__restrict__ 
         if (pn < p_end) load_page_warp<HD>(ks, k_pool + nbase, lane);
         cp_async_commit();                     // (possibly empty) group: keeps the wait counts uniform
         if (rp * PAGE + PAGE - 1 <= pos && rp * PAGE >= lo_key)
-            softmax_update<HD / 8, false>(s, o, m, l, scale * LOG2E, rp * PAGE, lo, hi, lane);
+            softmax_update<HD / 8, false>(s, o, m, l, scale * LOG2E, rp * PAGE, lo, hi, lane, 0, cap_log2, cap_in);
         else
-            softmax_update<HD / 8, true>(s, o, m, l, scale * LOG2E, rp * PAGE, lo, hi, lane, keep);
+            softmax_update<HD / 8, true>(s, o, m, l, scale * LOG2E, rp * PAGE, lo, hi, lane, keep, cap_log2, cap_in);
         cp_async_wait<1>();                    // V of this page has landed
         __syncwarp();
         if (newest) {
@@ -370,11 +382,14 @@ static int launch_decode_kernel(dim3 grid, int cluster_x, cudaStream_t stream, c
 template <int HD>
 static int launch_decode(const void *q, int ldq, void *out, int ldo, const int *positions, const int *block_table,
                          int table_width, const void *k_pool, const void *v_pool, int B, int H, int KV, float scale,
-                         int window, int keep_first, int n_splits, float *part_o, float *part_ml, cudaStream_t stream) {
+                         int window, int keep_first, int n_splits, float *part_o, float *part_ml, cudaStream_t stream,
+                         float softcap = 0.f, const float *sinks = nullptr) {
     int G = H / KV;
     dim3 grid(n_splits, KV * ((G + 15) / 16), B);
     RopeArgs extra{};
     extra.keep_first = keep_first;
+    extra.softcap = softcap;
+    extra.sinks = sinks;
     // 2, 4 or 8 splits without scratch memory: merged inside a cluster
     bool cluster = !part_o && (n_splits == 2 || n_splits == 4 || n_splits == 8);
     if (n_splits == 1 || cluster)
@@ -393,18 +408,28 @@ static int launch_decode(const void *q, int ldq, void *out, int ldo, const int *
 // path; pass null pointers with n_splits 1, 2, 4 or 8 for the path that needs no scratch.
 // Takes HD 64 and 128 and pages of 64; anything else returns FG_ERR_BAD_SIZE.
 // keep_first (with a window): the first keep_first keys of the sequence stay visible.
+// softcap > 0: capped scores; sinks (or null): a float per query head that joins the softmax's denominator.
+extern "C" int fg_attention_decode_ext(const void *q, int ldq, void *out, int ldo, const int *positions,
+                                        const int *block_table, int table_width, const void *k_pool, const void *v_pool,
+                                        int B, int H, int KV, int hd, int page_size, float scale, int window, int keep_first,
+                                        int n_splits, float *part_o, float *part_ml, float softcap, const float *sinks,
+                                        cudaStream_t stream) {
+    if (B <= 0) return 0;
+    if (KV <= 0 || H <= 0 || keep_first < 0 || softcap < 0.f) return FG_ERR_BAD_SIZE;
+    if (page_size != PAGE || H % KV || n_splits < 1 || B > 65535 || ldq % 2 || ((uintptr_t)q & 3)) return FG_ERR_BAD_SIZE;
+    if ((part_o == nullptr) != (part_ml == nullptr)) return FG_ERR_BAD_SIZE;
+    if (!part_o && n_splits != 1 && n_splits != 2 && n_splits != 4 && n_splits != 8) return FG_ERR_BAD_SIZE;
+    if (hd == 64) return launch_decode<64>(q, ldq, out, ldo, positions, block_table, table_width, k_pool, v_pool, B, H, KV, scale, window, keep_first, n_splits, part_o, part_ml, stream, softcap, sinks);
+    if (hd == 128) return launch_decode<128>(q, ldq, out, ldo, positions, block_table, table_width, k_pool, v_pool, B, H, KV, scale, window, keep_first, n_splits, part_o, part_ml, stream, softcap, sinks);
+    return FG_ERR_BAD_SIZE;
+}
+
 extern "C" int fg_attention_decode_kept(const void *q, int ldq, void *out, int ldo, const int *positions,
                                         const int *block_table, int table_width, const void *k_pool, const void *v_pool,
                                         int B, int H, int KV, int hd, int page_size, float scale, int window, int keep_first,
                                         int n_splits, float *part_o, float *part_ml, cudaStream_t stream) {
-    if (B <= 0) return 0;
-    if (KV <= 0 || H <= 0 || keep_first < 0) return FG_ERR_BAD_SIZE;
-    if (page_size != PAGE || H % KV || n_splits < 1 || B > 65535 || ldq % 2 || ((uintptr_t)q & 3)) return FG_ERR_BAD_SIZE;
-    if ((part_o == nullptr) != (part_ml == nullptr)) return FG_ERR_BAD_SIZE;
-    if (!part_o && n_splits != 1 && n_splits != 2 && n_splits != 4 && n_splits != 8) return FG_ERR_BAD_SIZE;
-    if (hd == 64) return launch_decode<64>(q, ldq, out, ldo, positions, block_table, table_width, k_pool, v_pool, B, H, KV, scale, window, keep_first, n_splits, part_o, part_ml, stream);
-    if (hd == 128) return launch_decode<128>(q, ldq, out, ldo, positions, block_table, table_width, k_pool, v_pool, B, H, KV, scale, window, keep_first, n_splits, part_o, part_ml, stream);
-    return FG_ERR_BAD_SIZE;
+    return fg_attention_decode_ext(q, ldq, out, ldo, positions, block_table, table_width, k_pool, v_pool, B, H, KV, hd, page_size, scale,
+                                   window, keep_first, n_splits, part_o, part_ml, 0.f, nullptr, stream);
 }
 
 extern "C" int fg_attention_decode(const void *q, int ldq, void *out, int ldo, const int *positions,

@@ -99,10 +99,18 @@ __device__ __forceinline__ float ex2(float x) {
 // MASK: `key0` is the position of the tile's first key and keys outside [lo[i], hi[i]] are
 // masked; without MASK every key of the tile is visible to every row (no compares).
 // On return s holds the probabilities 2^(score - m_new) and o, l are rescaled.
+// cap_log2 > 0: scores are capped, score <- cap * tanh(scale * raw / cap), written here in the base-2 domain as
+// cap_log2 * tanh(raw * cap_in) with cap_log2 = cap * log2(e) and cap_in = scale / cap.
+// A sink (a key without a value that joins the denominator once) needs nothing here: the caller starts ONE of the running
+// (m, l) pairs that are merged into a row's result at (sink * log2(e), 1) instead of (-inf, 0).
+// tanh(x) = 1 - 2 / (1 + 2^(2 x log2(e))): two special-function instructions, absolute error about 2e-7
+__device__ __forceinline__ float tanh_fast(float x) { return 1.0f - __fdividef(2.0f, 1.0f + ex2(x * (2.0f * 1.4426950408889634f))); }
+
 template <int NO, bool MASK>
 __device__ __forceinline__ void softmax_update(float (&s)[8][4], float (&o)[NO][4], float (&m)[2], float (&l)[2],
                                                float scale_log2, int key0, const int (&lo)[2], const int (&hi)[2], int lane,
-                                               int keep = 0 /* keys below it stay visible in front of lo */) {
+                                               int keep = 0 /* keys below it stay visible in front of lo */,
+                                               float cap_log2 = 0.f, float cap_in = 0.f) {
     const int c0 = key0 + 2 * (lane & 3);
     float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
@@ -110,7 +118,7 @@ __device__ __forceinline__ void softmax_update(float (&s)[8][4], float (&o)[NO][
 #pragma unroll
         for (int e = 0; e < 4; e++) {
             int i = e >> 1, key = c0 + 8 * j + (e & 1);
-            float v = s[j][e] * scale_log2;
+            float v = cap_log2 > 0.f ? cap_log2 * tanh_fast(s[j][e] * cap_in) : s[j][e] * scale_log2;
             if (MASK) v = ((key >= lo[i] || key < keep) && key <= hi[i]) ? v : -INFINITY;
             s[j][e] = v;
             mx[i] = fmaxf(mx[i], v);

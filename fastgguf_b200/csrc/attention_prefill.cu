@@ -31,7 +31,7 @@ attn_prefill_kernel(const bf16 *__restrict__ q, int ldq, bf16 *__restrict__ out,
                     const int *__restrict__ cu_rows, const int *__restrict__ seq_start,
                     const int *__restrict__ block_table, int table_width,
                     const bf16 *__restrict__ k_pool, const bf16 *__restrict__ v_pool,
-                    int KV, int G, float scale, int window, int keep_first) {
+                    int KV, int G, float scale, int window, int keep_first, float softcap, const float *__restrict__ sinks) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int TILE_BYTES = PAGE * HD * 2;
     constexpr int PF_ROWS = PF_WARPS * 16;
@@ -94,6 +94,13 @@ attn_prefill_kernel(const bf16 *__restrict__ q, int ldq, bf16 *__restrict__ out,
 #pragma unroll
     for (int d = 0; d < HD / 8; d++) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    if (sinks) {
+        // a sink per query head joins the denominator once: the running maximum and sum start at (sink, 1)
+#pragma unroll
+        for (int i = 0; i < 2; i++)
+            if (valid[i]) { m[i] = sinks[kvh * G + g_[i]] * LOG2E; l[i] = 1.f; }
+    }
+    const float cap_log2 = softcap > 0.f ? softcap * LOG2E : 0.f, cap_in = softcap > 0.f ? scale / softcap : 0.f;
 
     const uint32_t s0 = smem_addr(smem);
     auto kaddr = [&](int st) { return s0 + st * 2 * TILE_BYTES; };
@@ -122,9 +129,9 @@ attn_prefill_kernel(const bf16 *__restrict__ q, int ldq, bf16 *__restrict__ out,
             qk_page<HD>(s, qf, kaddr(st), lane);
             // only pages that hold a row's own position (or a window's edge) need the mask
             if (rp * PAGE + PAGE - 1 <= warp_min_hi && rp * PAGE >= warp_max_lo)
-                softmax_update<HD / 8, false>(s, o, m, l, scale * LOG2E, rp * PAGE, lo, hi, lane);
+                softmax_update<HD / 8, false>(s, o, m, l, scale * LOG2E, rp * PAGE, lo, hi, lane, 0, cap_log2, cap_in);
             else
-                softmax_update<HD / 8, true>(s, o, m, l, scale * LOG2E, rp * PAGE, lo, hi, lane, keep);
+                softmax_update<HD / 8, true>(s, o, m, l, scale * LOG2E, rp * PAGE, lo, hi, lane, keep, cap_log2, cap_in);
             pv_page<HD>(o, s, vaddr(st), lane);
         }
         __syncthreads();                       // the stage is overwritten by the load after next
@@ -145,7 +152,8 @@ attn_prefill_kernel(const bf16 *__restrict__ q, int ldq, bf16 *__restrict__ out,
 template <int HD, int PF_WARPS>
 static int launch_prefill(const void *q, int ldq, void *out, int ldo, const int *cu_rows, const int *seq_start,
                           const int *block_table, int table_width, const void *k_pool, const void *v_pool,
-                          int n_seq, int max_new, int H, int KV, float scale, int window, int keep_first, cudaStream_t stream) {
+                          int n_seq, int max_new, int H, int KV, float scale, int window, int keep_first, float softcap, const float *sinks,
+                          cudaStream_t stream) {
     constexpr int smem = 2 * 2 * PAGE * HD * 2;
     static FgPerDevice configured;
     if (fg_needs_setup(configured)) {
@@ -155,23 +163,34 @@ static int launch_prefill(const void *q, int ldq, void *out, int ldo, const int 
     int G = H / KV, Gc = G < 16 ? G : 16, TQ = PF_WARPS * 16 / Gc;
     dim3 grid((max_new + TQ - 1) / TQ, KV * ((G + Gc - 1) / Gc), n_seq);
     return fg_launch(attn_prefill_kernel<HD, PF_WARPS>, grid, dim3(PF_WARPS * 32), (size_t)smem, stream, (const bf16 *)q, ldq, (bf16 *)out, ldo, cu_rows,
-        seq_start, block_table, table_width, (const bf16 *)k_pool, (const bf16 *)v_pool, KV, G, scale, window, keep_first);
+        seq_start, block_table, table_width, (const bf16 *)k_pool, (const bf16 *)v_pool, KV, G, scale, window, keep_first, softcap, sinks);
 }
 
 // q: [rows, ldq] bf16 rows of all sequences one after another (cu_rows[b] = first row of sequence b,
 // seq_start[b] = its length before the step); pools [pages, KV, 64, HD] bf16; out [rows, ldo] bf16.
 // max_new: most rows any sequence brings.  Takes HD 64 and 128 and pages of 64.
 // keep_first (with a window): the first keep_first keys of a sequence stay visible to every row.
+// softcap > 0: capped scores; sinks (or null): a float per query head that joins the softmax's denominator.
+extern "C" int fg_attention_prefill_ext(const void *q, int ldq, void *out, int ldo, const int *cu_rows,
+                                         const int *seq_start, const int *block_table, int table_width,
+                                         const void *k_pool, const void *v_pool, int n_seq, int max_new, int H, int KV,
+                                         int hd, int page_size, float scale, int window, int keep_first, float softcap,
+                                         const float *sinks, cudaStream_t stream) {
+    if (n_seq <= 0 || max_new <= 0) return 0;
+    if (softcap < 0.f) return FG_ERR_BAD_SIZE;
+    if (keep_first < 0 || page_size != PAGE || H % KV || n_seq > 65535 || ldq % 2 || ldo % 2 || ((uintptr_t)q & 3) || ((uintptr_t)out & 3))
+        return FG_ERR_BAD_SIZE;
+    if (hd == 64) return launch_prefill<64, 8>(q, ldq, out, ldo, cu_rows, seq_start, block_table, table_width, k_pool, v_pool, n_seq, max_new, H, KV, scale, window, keep_first, softcap, sinks, stream);
+    if (hd == 128) return launch_prefill<128, 4>(q, ldq, out, ldo, cu_rows, seq_start, block_table, table_width, k_pool, v_pool, n_seq, max_new, H, KV, scale, window, keep_first, softcap, sinks, stream);
+    return FG_ERR_BAD_SIZE;
+}
+
 extern "C" int fg_attention_prefill_kept(const void *q, int ldq, void *out, int ldo, const int *cu_rows,
                                          const int *seq_start, const int *block_table, int table_width,
                                          const void *k_pool, const void *v_pool, int n_seq, int max_new, int H, int KV,
                                          int hd, int page_size, float scale, int window, int keep_first, cudaStream_t stream) {
-    if (n_seq <= 0 || max_new <= 0) return 0;
-    if (keep_first < 0 || page_size != PAGE || H % KV || n_seq > 65535 || ldq % 2 || ldo % 2 || ((uintptr_t)q & 3) || ((uintptr_t)out & 3))
-        return FG_ERR_BAD_SIZE;
-    if (hd == 64) return launch_prefill<64, 8>(q, ldq, out, ldo, cu_rows, seq_start, block_table, table_width, k_pool, v_pool, n_seq, max_new, H, KV, scale, window, keep_first, stream);
-    if (hd == 128) return launch_prefill<128, 4>(q, ldq, out, ldo, cu_rows, seq_start, block_table, table_width, k_pool, v_pool, n_seq, max_new, H, KV, scale, window, keep_first, stream);
-    return FG_ERR_BAD_SIZE;
+    return fg_attention_prefill_ext(q, ldq, out, ldo, cu_rows, seq_start, block_table, table_width, k_pool, v_pool, n_seq, max_new, H,
+                                    KV, hd, page_size, scale, window, keep_first, 0.f, nullptr, stream);
 }
 
 extern "C" int fg_attention_prefill(const void *q, int ldq, void *out, int ldo, const int *cu_rows,

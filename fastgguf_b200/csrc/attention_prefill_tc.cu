@@ -167,9 +167,14 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
     asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
     return r;
 }
-template <bool MASKED>
+// tanh(x) = 1 - 2 / (1 + 2^(2 x log2(e))): two special-function instructions, absolute error about 2e-7
+__device__ __forceinline__ float tanh_fast(float x) { return 1.0f - __fdividef(2.0f, 1.0f + ex2(x * (2.0f * 1.4426950408889634f))); }
+// CAP: capped scores, cap * tanh(scale * raw / cap); in the base-2 domain cap_log2 * tanh(raw * cap_in) with
+// cap_log2 = cap * log2(e) (passed as `scale`) and cap_in = scale / cap.  tanh keeps the order of the raw scores, so the
+// largest raw score still names the largest capped one.
+template <bool MASKED, bool CAP = false>
 __device__ __forceinline__ void softmax_chunk(const float (&v)[32], int key, int lo, int hi, float scale, float neg_base,
-                                              float &mx_raw, float &acc, uint32_t (&w)[16]) {
+                                              float &mx_raw, float &acc, uint32_t (&w)[16], float cap_in = 0.f) {
 #pragma unroll
     for (int i = 0; i < 32; i += 2) {
         float a = v[i], b = v[i + 1];
@@ -178,7 +183,14 @@ __device__ __forceinline__ void softmax_chunk(const float (&v)[32], int key, int
             if (key + i + 1 < lo || key + i + 1 > hi) b = -INFINITY;
         }
         mx_raw = max3(mx_raw, a, b);
-        const float p0 = ex2(fmaf(a, scale, neg_base)), p1 = ex2(fmaf(b, scale, neg_base));
+        float p0, p1;
+        if (CAP) {
+            p0 = a == -INFINITY ? 0.f : ex2(fmaf(tanh_fast(a * cap_in), scale, neg_base));
+            p1 = b == -INFINITY ? 0.f : ex2(fmaf(tanh_fast(b * cap_in), scale, neg_base));
+        } else {
+            p0 = ex2(fmaf(a, scale, neg_base));
+            p1 = ex2(fmaf(b, scale, neg_base));
+        }
         acc += p0 + p1;
         __nv_bfloat162 t = __floats2bfloat162_rn(p0, p1);
         w[i >> 1] = *(uint32_t *)&t;
@@ -200,7 +212,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
                        const bf16 *__restrict__ q, int ldq, bf16 *__restrict__ out, int ldo,
                        const int *__restrict__ cu_rows, const int *__restrict__ seq_start,
                        const int *__restrict__ block_table, int table_width, int KV, int G, float scale_log2, int window,
-                       int keep_first, int test_skip_copy) {
+                       int keep_first, int test_skip_copy, float cap_log2, float cap_in, const float *__restrict__ sinks) {
     constexpr int CH = HD / 64;                        // 64-wide chunks of the head dimension
     constexpr int KEYS = PIPE ? 64 : (HD > 64 ? 64 : 128), NPG = KEYS / PAGE;      // keys and pages per iteration
     constexpr int NS = PIPE ? 2 : 1;                   // score tiles in tensor memory, P tiles in shared memory
@@ -377,6 +389,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
         // the wait for the P V of this thread's previous iteration names a phase by its parity: PP counts the set's own
         auto o_parity = [&](int j_prev) { return (uint32_t)((PP ? j_prev >> 1 : j_prev) & 1); };
         float m = -INFINITY, l = 0.f;
+        // a sink per query head joins the denominator once: this row's running maximum and sum start at (sink, 1) (PP: in set 0)
+        if (sinks && valid && set == 0) { m = sinks[kvh * G + g_row] * LOG2E; l = 1.f; }
+        // the score in the base-2 domain that the largest raw score of a tile stands for
+        auto scaled = [&](float raw) { return cap_log2 > 0.f ? (raw == -INFINITY ? -INFINITY : cap_log2 * tanh_fast(raw * cap_in)) : raw * scale_log2; };
         bool ok = true;
         int j_last = -1;
         for (int j = set; j < n_iter; j += step) {
@@ -400,7 +416,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
                 const float neg_base = -base;
                 auto chunk = [&](int c, const float (&v)[32]) {
                     uint32_t w[16];
-                    if (any_masked) softmax_chunk<true>(v, key0 + c * 32, masked ? lo_j : INT_MIN, masked ? hi_j : INT_MAX, scale_log2, neg_base, mx_raw, acc, w);
+                    if (cap_log2 > 0.f) softmax_chunk<true, true>(v, key0 + c * 32, masked ? lo_j : INT_MIN, masked ? hi_j : INT_MAX, cap_log2, neg_base, mx_raw, acc, w, cap_in);
+                    else if (any_masked) softmax_chunk<true>(v, key0 + c * 32, masked ? lo_j : INT_MIN, masked ? hi_j : INT_MAX, scale_log2, neg_base, mx_raw, acc, w);
                     else softmax_chunk<false>(v, 0, 0, 0, scale_log2, neg_base, mx_raw, acc, w);
                     // 32 keys = four 16-byte chunks of this row, in the 64-key chunk c / 2
 #pragma unroll
@@ -439,7 +456,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
             if (!redo) {
                 float mx_raw = -INFINITY;
                 pass(m, mx_raw, sum);
-                redo = __any_sync(0xffffffffu, mx_raw * scale_log2 > m + 8.0f);
+                redo = __any_sync(0xffffffffu, scaled(mx_raw) > m + 8.0f);
             }
             float m_keep = m;
             if (redo) {
@@ -456,7 +473,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
                         mx_raw = fmaxf(mx_raw, x);
                     }
                 }
-                const float m_new = fmaxf(m, mx_raw * scale_log2);            // the scale is positive
+                const float m_new = fmaxf(m, scaled(mx_raw));                 // the scale is positive
                 corr = m == -INFINITY ? 1.f : ex2(m - m_new);                 // m_new >= m; nothing seen yet: keep zeros
                 const float base = m_new == -INFINITY ? 0.f : m_new;
                 sum = 0.f;
@@ -576,7 +593,8 @@ static int pool_map(CUtensorMap *map, const void *pool, long long rows, int hd) 
 template <int HD, bool PIPE, bool PP>
 static int launch_tc(const CUtensorMap &tmK, const CUtensorMap &tmV, const void *q, int ldq, void *out, int ldo,
                      const int *cu_rows, const int *seq_start, const int *block_table, int table_width, int n_seq,
-                     int max_new, int H, int KV, float scale, int window, int keep_first, cudaStream_t stream) {
+                     int max_new, int H, int KV, float scale, int window, int keep_first, float softcap, const float *sinks,
+                     cudaStream_t stream) {
     constexpr int KEYS = PIPE ? 64 : (HD > 64 ? 64 : 128);
     constexpr int smem = ROWS * HD * 2 + 2 * KEYS * HD * 2 + (PIPE ? 2 : 1) * ROWS * KEYS * 2 + 1024;
     // the attributes belong to the function on ONE device: set them once on every device that launches
@@ -592,16 +610,19 @@ static int launch_tc(const CUtensorMap &tmK, const CUtensorMap &tmV, const void 
     int G = H / KV, Gc = G < 16 ? G : 16, TQ = ROWS / Gc;
     dim3 grid(KV * ((G + Gc - 1) / Gc), (max_new + TQ - 1) / TQ, n_seq);
     return fg_launch(attn_prefill_tc_kernel<HD, PIPE, PP>, grid, dim3(ATT_THREADS(PP)), (size_t)smem, stream, tmK, tmV, (const bf16 *)q, ldq,
-                     (bf16 *)out, ldo, cu_rows, seq_start, block_table, table_width, KV, G, scale * LOG2E, window, keep_first, g_test_skip_copy);
+                     (bf16 *)out, ldo, cu_rows, seq_start, block_table, table_width, KV, G, scale * LOG2E, window, keep_first, g_test_skip_copy,
+                     softcap > 0.f ? softcap * LOG2E : 0.f, softcap > 0.f ? scale / softcap : 0.f, sinks);
 }
 
 // Arguments as fg_attention_prefill_kept, plus the number of pages in the pools.  Takes HD 64 and 128.
-extern "C" int fg_attention_prefill_tc_kept(const void *q, int ldq, void *out, int ldo, const int *cu_rows,
-                                            const int *seq_start, const int *block_table, int table_width,
-                                            const void *k_pool, const void *v_pool, int n_pages, int n_seq, int max_new,
-                                            int H, int KV, int hd, int page_size, float scale, int window, int keep_first,
-                                            cudaStream_t stream) {
+// softcap > 0: capped scores; sinks (or null): a float per query head that joins the softmax's denominator.
+extern "C" int fg_attention_prefill_tc_ext(const void *q, int ldq, void *out, int ldo, const int *cu_rows,
+                                           const int *seq_start, const int *block_table, int table_width,
+                                           const void *k_pool, const void *v_pool, int n_pages, int n_seq, int max_new,
+                                           int H, int KV, int hd, int page_size, float scale, int window, int keep_first,
+                                           float softcap, const float *sinks, cudaStream_t stream) {
     if (n_seq <= 0 || max_new <= 0) return 0;
+    if (softcap < 0.f) return FG_ERR_BAD_SIZE;
     if (keep_first < 0 || page_size != PAGE || H % KV || n_seq > 65535 || ldq % 8 || ldo % 8 || ((uintptr_t)q & 15) || ((uintptr_t)out & 15) ||
         ((uintptr_t)k_pool & 15) || ((uintptr_t)v_pool & 15) || (hd != 64 && hd != 128))
         return FG_ERR_BAD_SIZE;
@@ -622,10 +643,19 @@ extern "C" int fg_attention_prefill_tc_kept(const void *q, int ldq, void *out, i
     const bool pipe = g_variant >= 0 ? ((g_variant >> (hd == 64 ? 0 : 1)) & 1) != 0 : true;
     const bool pp = hd == 64 && pipe && (g_variant >= 0 ? (g_variant & 4) != 0 : (long long)n_seq * max_new >= 3072);
 #define TC_RUN(HD, PIPE, PP) launch_tc<HD, PIPE, PP>(tmK, tmV, q, ldq, out, ldo, cu_rows, seq_start, block_table, table_width, \
-                                                     n_seq, max_new, H, KV, scale, window, keep_first, stream)
+                                                     n_seq, max_new, H, KV, scale, window, keep_first, softcap, sinks, stream)
     if (hd == 64) return pipe ? (pp ? TC_RUN(64, true, true) : TC_RUN(64, true, false)) : TC_RUN(64, false, false);
     return pipe ? TC_RUN(128, true, false) : TC_RUN(128, false, false);
 #undef TC_RUN
+}
+
+extern "C" int fg_attention_prefill_tc_kept(const void *q, int ldq, void *out, int ldo, const int *cu_rows,
+                                            const int *seq_start, const int *block_table, int table_width,
+                                            const void *k_pool, const void *v_pool, int n_pages, int n_seq, int max_new,
+                                            int H, int KV, int hd, int page_size, float scale, int window, int keep_first,
+                                            cudaStream_t stream) {
+    return fg_attention_prefill_tc_ext(q, ldq, out, ldo, cu_rows, seq_start, block_table, table_width, k_pool, v_pool, n_pages, n_seq,
+                                       max_new, H, KV, hd, page_size, scale, window, keep_first, 0.f, nullptr, stream);
 }
 
 extern "C" int fg_attention_prefill_tc(const void *q, int ldq, void *out, int ldo, const int *cu_rows,

@@ -17,7 +17,7 @@
 
 // cos/sin: [positions, tbl_half] float32, column i = pair i.
 template <typename T>
-__global__ void __launch_bounds__(PREP_THREADS)
+__global__ void __launch_bounds__(1024)
 qkv_prepare_kernel(const float *__restrict__ proj, int ld, const float *__restrict__ bias, const float *__restrict__ conv_w, int taps,
                    const float *__restrict__ conv_state, const float *__restrict__ qn_w, const float *__restrict__ kn_w, float eps,
                    const float *__restrict__ cos_t, const float *__restrict__ sin_t, int tbl_half, int rot_dims,
@@ -28,14 +28,14 @@ qkv_prepare_kernel(const float *__restrict__ proj, int ld, const float *__restri
     __shared__ float scratch[32];
     pdl_launch_dependents();
     pdl_wait();
-    const int m = blockIdx.x, tid = threadIdx.x;
+    const int m = blockIdx.x, tid = threadIdx.x, nthr = blockDim.x;
     const int Cq = H * hd, Ck = KV * hd, C = Cq + Ck + KV * hdv;
     const int seq = row_seq[m], pos = positions[m];
     const int i_step = m - cu_rows[seq];                 // the token's index among the step's tokens of its sequence
     const float *mine = proj + (size_t)m * ld;
     if (conv_w) {
         const float *st = conv_state + (size_t)slots[seq] * (taps - 1) * C;
-        for (int c = tid; c < C; c += PREP_THREADS) {
+        for (int c = tid; c < C; c += nthr) {
             const float b = bias ? bias[c] : 0.f;
             float acc = 0.f;
             for (int j = 0; j < taps; j++) {
@@ -48,24 +48,24 @@ qkv_prepare_kernel(const float *__restrict__ proj, int ld, const float *__restri
             row[c] = acc;
         }
     } else {
-        for (int c = tid; c < C; c += PREP_THREADS) row[c] = mine[c] + (bias ? bias[c] : 0.f);
+        for (int c = tid; c < C; c += nthr) row[c] = mine[c] + (bias ? bias[c] : 0.f);
     }
     __syncthreads();
     if (qn_w) {
         float sq = 0.f, sk = 0.f;
-        for (int c = tid; c < Cq; c += PREP_THREADS) sq = fmaf(row[c], row[c], sq);
-        for (int c = tid; c < Ck; c += PREP_THREADS) sk = fmaf(row[Cq + c], row[Cq + c], sk);
+        for (int c = tid; c < Cq; c += nthr) sq = fmaf(row[c], row[c], sq);
+        for (int c = tid; c < Ck; c += nthr) sk = fmaf(row[Cq + c], row[Cq + c], sk);
         sq = block_sum(sq, scratch);
         sk = block_sum(sk, scratch);
         const float iq = 1.0f / sqrtf(sq / (float)Cq + eps), ik = 1.0f / sqrtf(sk / (float)Ck + eps);
-        for (int c = tid; c < Cq; c += PREP_THREADS) row[c] = row[c] * iq * qn_w[c];
-        for (int c = tid; c < Ck; c += PREP_THREADS) row[Cq + c] = row[Cq + c] * ik * kn_w[c];
+        for (int c = tid; c < Cq; c += nthr) row[c] = row[c] * iq * qn_w[c];
+        for (int c = tid; c < Ck; c += nthr) row[Cq + c] = row[Cq + c] * ik * kn_w[c];
         __syncthreads();
     }
     const int rh = rot_dims / 2;
     if (rh > 0) {
         const float *cs = cos_t + (size_t)pos * tbl_half, *sn = sin_t + (size_t)pos * tbl_half;
-        for (int e = tid; e < (H + KV) * rh; e += PREP_THREADS) {
+        for (int e = tid; e < (H + KV) * rh; e += nthr) {
             const int head = e / rh, i = e - head * rh;
             float *p = row + (size_t)head * hd + 2 * i;   // q heads and k heads lie one after another, all of size hd
             const float a = p[0], b = p[1], c = cs[i], s = sn[i];
@@ -74,14 +74,14 @@ qkv_prepare_kernel(const float *__restrict__ proj, int ld, const float *__restri
         }
         __syncthreads();
     }
-    for (int c = tid; c < Cq; c += PREP_THREADS) q_out[(size_t)m * ldq + c] = from_f32<T>(row[c]);
+    for (int c = tid; c < Cq; c += nthr) q_out[(size_t)m * ldq + c] = from_f32<T>(row[c]);
     if (k_pool) {
         const int page = block_table[(size_t)seq * table_width + pos / page_size], off = pos % page_size;
-        for (int c = tid; c < Ck; c += PREP_THREADS) {
+        for (int c = tid; c < Ck; c += nthr) {
             const int kvh = c / hd, d = c - kvh * hd;
             k_pool[(((size_t)page * KV + kvh) * page_size + off) * hd + d] = from_f32<T>(row[Cq + c]);
         }
-        for (int c = tid; c < KV * hdv; c += PREP_THREADS) {
+        for (int c = tid; c < KV * hdv; c += nthr) {
             const int kvh = c / hdv, d = c - kvh * hdv;
             v_pool[(((size_t)page * KV + kvh) * page_size + off) * hdv + d] = from_f32<T>(row[Cq + Ck + c]);
         }
@@ -222,6 +222,60 @@ head_gemm_kernel(const void *__restrict__ A, int a_dtype, int lda, int a_stride,
         }
 }
 
+// The same contraction for a few rows (a decode step): every weight is read once, 16-byte or coalesced, for all rows.
+// TRANSPOSED: a thread per output n (a stored row runs along n, so neighbouring threads read neighbouring numbers), sums along
+// k in order; else a warp per output n with its lanes along k (a stored row runs along k) and a shuffle tree at the end.
+#define HV_ROWS 16
+template <bool TRANSPOSED>
+__global__ void __launch_bounds__(256)
+head_gemv_kernel(const void *__restrict__ A, int a_dtype, int lda, int a_stride, const void *__restrict__ W, int w_dtype, int ldw,
+                 void *__restrict__ Cm, int c_dtype, int ldc, int c_stride, const float *__restrict__ gate, int ldg, int M, int N, int K) {
+    extern __shared__ float as[];                       // [M][K]
+    pdl_launch_dependents();
+    pdl_wait();
+    const int h = blockIdx.y;
+    for (int e = threadIdx.x; e < M * K; e += 256) {
+        const int m = e / K, k = e - m * K;
+        as[e] = load_as(A, a_dtype, (size_t)m * lda + (size_t)h * a_stride + k);
+    }
+    __syncthreads();
+    float acc[HV_ROWS];
+#pragma unroll
+    for (int m = 0; m < HV_ROWS; m++) acc[m] = 0.f;
+    int n;
+    if (TRANSPOSED) {
+        n = blockIdx.x * 256 + threadIdx.x;
+        if (n >= N) return;
+        for (int k = 0; k < K; k++) {
+            const float w = load_as(W, w_dtype, ((size_t)h * K + k) * ldw + n);
+#pragma unroll
+            for (int m = 0; m < HV_ROWS; m++)
+                if (m < M) acc[m] = fmaf(as[m * K + k], w, acc[m]);
+        }
+    } else {
+        const int lane = threadIdx.x & 31;
+        n = blockIdx.x * 8 + (threadIdx.x >> 5);
+        if (n >= N) return;
+        for (int k = lane; k < K; k += 32) {
+            const float w = load_as(W, w_dtype, ((size_t)h * N + n) * ldw + k);
+#pragma unroll
+            for (int m = 0; m < HV_ROWS; m++)
+                if (m < M) acc[m] = fmaf(as[m * K + k], w, acc[m]);
+        }
+#pragma unroll
+        for (int m = 0; m < HV_ROWS; m++)
+            if (m < M) acc[m] = warp_sum(acc[m]);
+        if (lane != 0) return;
+    }
+#pragma unroll
+    for (int m = 0; m < HV_ROWS; m++) {
+        if (m >= M) break;
+        float v = acc[m];
+        if (gate) v *= 1.0f / (1.0f + expf(-gate[(size_t)m * ldg + (size_t)h * N + n]));
+        store_as(Cm, c_dtype, (size_t)m * ldc + (size_t)h * c_stride + n, v);
+    }
+}
+
 extern "C" int fg_qkv_prepare(const float *proj, int ld, const float *bias, const float *conv_w, int taps, const float *conv_state,
                               const float *qn_w, const float *kn_w, float eps, const float *cos_t, const float *sin_t, int tbl_half,
                               int rot_dims, const int *positions, const int *row_seq, const int *cu_rows, const int *slots,
@@ -239,12 +293,15 @@ extern "C" int fg_qkv_prepare(const float *proj, int ld, const float *bias, cons
                                         : cudaFuncSetAttribute(qkv_prepare_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         if (e != cudaSuccess) return (int)e;
     }
+    // few rows (a decode step) leave most of the GPU idle: a row's channels are then spread over more threads
+    const int C_all = H * hd + KV * (hd + hdv);
+    const int threads = (M < 64 && C_all >= 2048) ? 1024 : PREP_THREADS;
     if (dtype == FG_F32)
-        return fg_launch(qkv_prepare_kernel<float>, dim3(M), dim3(PREP_THREADS), smem, stream, proj, ld, bias, conv_w, taps, conv_state, qn_w, kn_w,
+        return fg_launch(qkv_prepare_kernel<float>, dim3(M), dim3(threads), smem, stream, proj, ld, bias, conv_w, taps, conv_state, qn_w, kn_w,
                          eps, cos_t, sin_t, tbl_half, rot_dims, positions, row_seq, cu_rows, slots, block_table, table_width, (float *)q_out,
                          ldq, (float *)k_pool, (float *)v_pool, H, KV, hd, hdv, page_size);
     if (dtype == FG_BF16)
-        return fg_launch(qkv_prepare_kernel<bf16>, dim3(M), dim3(PREP_THREADS), smem, stream, proj, ld, bias, conv_w, taps, conv_state, qn_w, kn_w,
+        return fg_launch(qkv_prepare_kernel<bf16>, dim3(M), dim3(threads), smem, stream, proj, ld, bias, conv_w, taps, conv_state, qn_w, kn_w,
                          eps, cos_t, sin_t, tbl_half, rot_dims, positions, row_seq, cu_rows, slots, block_table, table_width, (bf16 *)q_out, ldq,
                          (bf16 *)k_pool, (bf16 *)v_pool, H, KV, hd, hdv, page_size);
     return FG_ERR_BAD_DTYPE;
@@ -301,6 +358,14 @@ extern "C" int fg_head_gemm(const void *A, int a_dtype, int lda, int a_stride, c
     if (K <= 0 || H > 65535) return FG_ERR_BAD_SIZE;
     for (int d : {a_dtype, w_dtype, c_dtype})
         if (d != FG_F32 && d != FG_BF16) return FG_ERR_BAD_DTYPE;
+    if (M <= HV_ROWS && (size_t)M * K * sizeof(float) <= 48 * 1024) {
+        const size_t smem = (size_t)M * K * sizeof(float);
+        if (transposed)
+            return fg_launch(head_gemv_kernel<true>, dim3((N + 255) / 256, H), dim3(256), smem, stream, A, a_dtype, lda, a_stride, W, w_dtype, ldw, C,
+                             c_dtype, ldc, c_stride, gate, ldg, M, N, K);
+        return fg_launch(head_gemv_kernel<false>, dim3((N + 7) / 8, H), dim3(256), smem, stream, A, a_dtype, lda, a_stride, W, w_dtype, ldw, C, c_dtype,
+                         ldc, c_stride, gate, ldg, M, N, K);
+    }
     dim3 grid((N + HG_T - 1) / HG_T, (M + HG_T - 1) / HG_T, H);
     if (grid.y > 65535) return FG_ERR_BAD_SIZE;
     return fg_launch(head_gemm_kernel, grid, dim3(256), 0, stream, A, a_dtype, lda, a_stride, W, w_dtype, ldw, transposed, C, c_dtype, ldc, c_stride,

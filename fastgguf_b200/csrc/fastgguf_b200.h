@@ -107,6 +107,18 @@ int fg_rmsnorm_strided(const float *x, int ldx, const float *w, void *out, int o
                        cudaStream_t stream);
 int fg_head_gemm(const void *A, int a_dtype, int lda, int a_stride, const void *W, int w_dtype, int ldw, int transposed, void *C,
                  int c_dtype, int ldc, int c_stride, const float *gate, int ldg, int M, int N, int K, int H, cudaStream_t stream);
+/* latent attention on the cache of latents (attention_latent.cu) */
+long long fg_latent_decode_scratch_floats(int M, int H, int R, int n_splits);
+int fg_latent_decode(const void *q, int ldq, void *out, int ldo, int dtype, const int *positions, const int *row_seq,
+                     const int *block_table, int table_width, const void *k_pool, const void *v_pool, int M, int H, int R,
+                     int DR, int page_size, float scale, const float *sinks, int n_splits, float *part, cudaStream_t stream);
+int fg_seq_page_table(const int *cu_rows, int n_seq, int width, int page_size, int *table, cudaStream_t stream);
+int fg_latent_expand(const float *q, int ldq, const float *kv, int ldkv, int rot_at, const void *kp, int ldkp, const void *vp,
+                     int ldvp, const float *cos_t, const float *sin_t, int tbl_half, const int *positions, const int *row_seq,
+                     const int *table, int width, void *qx, void *Kx, void *Vx, int M, int H, int D, int DR, int DV,
+                     int page_size, cudaStream_t stream);
+int fg_gate_slice(const void *x, int ldx, int stride, const float *gate, int ldg, void *out, int ldo, int dtype, int M, int H,
+                  int DV, cudaStream_t stream);
 int fg_moe_logits(const void *x, int ldx, const void *W, int ldw, int dtype, float *z, int M, int X, int E, cudaStream_t stream);
 int fg_moe_gather(const void *x, int ldx, int dtype, const int *order, int top, void *xs, int P, int E, cudaStream_t stream);
 int fg_moe_act(const float *gu, const int *order, const float *pair_weight, void *y, int dtype, int P, int F, float limit,
@@ -155,6 +167,19 @@ int fg_attention_prefill(const void *q, int ldq, void *out, int ldo, const int *
                          const int *block_table, int table_width, const void *k_pool, const void *v_pool, int n_seq,
                          int max_new, int H, int KV, int hd, int page_size, float scale, int window, cudaStream_t stream);
 /* the three above with the first keep_first keys of a sequence visible in front of a window */
+/* the same with capped scores (softcap > 0) and a sink per query head (sinks, or null) */
+int fg_attention_decode_ext(const void *q, int ldq, void *out, int ldo, const int *positions, const int *block_table,
+                            int table_width, const void *k_pool, const void *v_pool, int B, int H, int KV, int hd,
+                            int page_size, float scale, int window, int keep_first, int n_splits, float *part_o,
+                            float *part_ml, float softcap, const float *sinks, cudaStream_t stream);
+int fg_attention_prefill_ext(const void *q, int ldq, void *out, int ldo, const int *cu_rows, const int *seq_start,
+                             const int *block_table, int table_width, const void *k_pool, const void *v_pool, int n_seq,
+                             int max_new, int H, int KV, int hd, int page_size, float scale, int window, int keep_first,
+                             float softcap, const float *sinks, cudaStream_t stream);
+int fg_attention_prefill_tc_ext(const void *q, int ldq, void *out, int ldo, const int *cu_rows, const int *seq_start,
+                                const int *block_table, int table_width, const void *k_pool, const void *v_pool,
+                                int n_pool_pages, int n_seq, int max_new, int H, int KV, int hd, int page_size, float scale,
+                                int window, int keep_first, float softcap, const float *sinks, cudaStream_t stream);
 int fg_attention_decode_kept(const void *q, int ldq, void *out, int ldo, const int *positions, const int *block_table,
                              int table_width, const void *k_pool, const void *v_pool, int B, int H, int KV, int hd,
                              int page_size, float scale, int window, int keep_first, int n_splits, float *part_o,

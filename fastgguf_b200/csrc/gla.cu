@@ -113,39 +113,49 @@ __device__ __forceinline__ void gla_cumulative_log_decay(const float *__restrict
     }
 }
 
-// 1. U[c, h] = sum_j (k_j * exp(b_n - b_j)) v_j^T and D[c, h] = exp(b_n).  One block per (chunk, head).
+// 1. U[c, h] = sum_j (k_j * exp(b_n - b_j)) v_j^T and D[c, h] = exp(b_n).  One block per (chunk, head); thread (g, j) owns
+// column j of U and rows g, g + G, ...: the chunk's values of column j wait in registers, the decayed keys of a row are read
+// from shared memory as four 16-byte broadcasts.
 __global__ void __launch_bounds__(GLA_THREADS)
 gla_chunk_state_kernel(const float *__restrict__ proj, int ld, const float *__restrict__ z, int ldz, const float *__restrict__ z_bias,
                        const int *__restrict__ chunk_row, const int *__restrict__ chunk_len, float *__restrict__ U, float *__restrict__ D,
                        int H, int dk, int dv, float inv_tau) {
-    extern __shared__ float sm[];
+    extern __shared__ __align__(16) float sm[];
     pdl_launch_dependents();
     pdl_wait();
     const int c = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
     const int r0 = chunk_row[c], n = chunk_len[c];
-    float *b = sm, *kd = b + GC * dk, *vs = kd + GC * dk;      // [GC][dk], [GC][dk], [GC][dv]
+    float *b = sm, *kd = b + GC * dk;                          // b: [GC][dk]; kd: [dk][GC], zero beyond the chunk's n tokens
     gla_cumulative_log_decay(z, ldz, z_bias, r0, n, h, dk, inv_tau, b, tid);
-    for (int e = tid; e < n * dv; e += GLA_THREADS) {
-        const int t = e / dv, j = e - t * dv;
-        vs[e] = proj[(size_t)(r0 + t) * ld + (size_t)2 * H * dk + (size_t)h * dv + j];
-    }
     __syncthreads();
-    for (int e = tid; e < n * dk; e += GLA_THREADS) {
-        const int t = e / dk, i = e - t * dk;
-        kd[e] = proj[(size_t)(r0 + t) * ld + (size_t)(H + h) * dk + i] * expf(b[(n - 1) * dk + i] - b[e]);
+    for (int e = tid; e < GC * dk; e += GLA_THREADS) {
+        const int i = e / GC, t = e - i * GC;
+        kd[e] = t < n ? proj[(size_t)(r0 + t) * ld + (size_t)(H + h) * dk + i] * expf(b[(n - 1) * dk + i] - b[t * dk + i]) : 0.f;
     }
     for (int i = tid; i < dk; i += GLA_THREADS) D[((size_t)c * H + h) * dk + i] = expf(b[(n - 1) * dk + i]);
     __syncthreads();
+    const int G = GLA_THREADS / dv;
+    if (tid >= G * dv) return;
+    const int j = tid % dv, g = tid / dv;
+    float v[GC];
+#pragma unroll
+    for (int t = 0; t < GC; t++) v[t] = t < n ? proj[(size_t)(r0 + t) * ld + (size_t)2 * H * dk + (size_t)h * dv + j] : 0.f;
     float *Uc = U + ((size_t)c * H + h) * dk * dv;
-    for (int e = tid; e < dk * dv; e += GLA_THREADS) {
-        const int i = e / dv, j = e - i * dv;
+    for (int i = g; i < dk; i += G) {
+        const float4 *kr = (const float4 *)(kd + i * GC);
         float acc = 0.f;
-        for (int t = 0; t < n; t++) acc = fmaf(kd[t * dk + i], vs[t * dv + j], acc);
-        Uc[e] = acc;
+#pragma unroll
+        for (int t4 = 0; t4 < GC / 4; t4++) {
+            const float4 k4 = kr[t4];
+            acc = fmaf(k4.x, v[4 * t4], acc); acc = fmaf(k4.y, v[4 * t4 + 1], acc);
+            acc = fmaf(k4.z, v[4 * t4 + 2], acc); acc = fmaf(k4.w, v[4 * t4 + 3], acc);
+        }
+        Uc[(size_t)i * dv + j] = acc;
     }
 }
 
-// 2. per (sequence, head, slice of the state): S <- D_c S + U_c over the sequence's chunks; U_c receives the state before c
+// 2. per (sequence, head, slice of the state): S <- D_c S + U_c over the sequence's chunks; U_c receives the state before c.
+// Eight chunks' loads are in flight before the eight dependent updates run.
 __global__ void __launch_bounds__(GLA_THREADS)
 gla_chunk_scan_kernel(float *__restrict__ U, const float *__restrict__ D, const int *__restrict__ seq_chunk0, const int *__restrict__ slots,
                       float *__restrict__ state, int H, int dk, int dv) {
@@ -156,30 +166,43 @@ gla_chunk_scan_kernel(float *__restrict__ U, const float *__restrict__ D, const 
     if (e >= dk * dv) return;
     const int i = e / dv;
     const int c0 = seq_chunk0[seq], c1 = seq_chunk0[seq + 1];
-    float *Sg = state + ((size_t)slots[seq] * H + h) * dk * dv;
+    const size_t hs = (size_t)dk * dv;
+    float *Sg = state + ((size_t)slots[seq] * H + h) * hs;
     float s = Sg[e];
-    for (int c = c0; c < c1; c++) {
-        float *Uc = U + ((size_t)c * H + h) * dk * dv;
-        const float u = Uc[e], d = D[((size_t)c * H + h) * dk + i];
-        Uc[e] = s;
-        s = fmaf(s, d, u);
+    for (int c = c0; c < c1; c += 8) {
+        float u[8], d[8];
+#pragma unroll
+        for (int k = 0; k < 8; k++) {
+            const bool in = c + k < c1;
+            u[k] = in ? U[((size_t)(c + k) * H + h) * hs + e] : 0.f;
+            d[k] = in ? D[((size_t)(c + k) * H + h) * dk + i] : 1.f;
+        }
+#pragma unroll
+        for (int k = 0; k < 8; k++) {
+            if (c + k < c1) U[((size_t)(c + k) * H + h) * hs + e] = s;
+            s = fmaf(s, d[k], u[k]);
+        }
     }
     Sg[e] = s;
 }
 
-// 3. outputs of a chunk.  One block per (chunk, head); P (= U after the scan) is the state in front of the chunk.
+// 3. outputs of a chunk.  One block per (chunk, head); P (= U after the scan) is the state in front of the chunk.  Thread
+// (g, j) owns column j of the chunk's GC outputs (in registers) and, of the sums over key channels and over earlier tokens,
+// the terms g, g + G, ...: the state is read ONCE, coalesced, straight from global memory; the groups' partial sums are
+// added in group order.
 template <typename TO>
 __global__ void __launch_bounds__(GLA_THREADS)
 gla_chunk_out_kernel(const float *__restrict__ proj, int ld, const float *__restrict__ z, int ldz, const float *__restrict__ z_bias,
                      const float *__restrict__ norm_w, TO *__restrict__ out, int ldo, const int *__restrict__ chunk_row,
                      const int *__restrict__ chunk_len, const float *__restrict__ P, int H, int dk, int dv, float inv_tau, float q_scale,
                      float eps) {
-    extern __shared__ float sm[];
+    extern __shared__ __align__(16) float sm[];
     pdl_launch_dependents();
     pdl_wait();
     const int c = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
     const int r0 = chunk_row[c], n = chunk_len[c];
-    float *b = sm, *qs = b + GC * dk, *ks = qs + GC * dk, *vs = ks + GC * dk, *A = vs + GC * dv, *os = A + GC * GC, *inv = os + GC * dv;
+    // b, qs, ks: [GC][dk]; qd: [dk][GC] = q_t * exp(b_t), zero beyond n; AT: [GC (u)][GC (t)] = A[t][u], zero where u > t
+    float *b = sm, *qs = b + GC * dk, *ks = qs + GC * dk, *qd = ks + GC * dk, *AT = qd + GC * dk, *part = AT + GC * GC, *os = part + GC * GLA_THREADS, *inv = os + GC * dv;
     gla_cumulative_log_decay(z, ldz, z_bias, r0, n, h, dk, inv_tau, b, tid);
     for (int e = tid; e < n * dk; e += GLA_THREADS) {
         const int t = e / dk, i = e - t * dk;
@@ -187,53 +210,83 @@ gla_chunk_out_kernel(const float *__restrict__ proj, int ld, const float *__rest
         qs[e] = row[(size_t)h * dk + i] * q_scale;
         ks[e] = row[(size_t)(H + h) * dk + i];
     }
-    for (int e = tid; e < n * dv; e += GLA_THREADS) {
-        const int t = e / dv, j = e - t * dv;
-        vs[e] = proj[(size_t)(r0 + t) * ld + (size_t)2 * H * dk + (size_t)h * dv + j];
-    }
     __syncthreads();
-    // scores inside the chunk: A[t][j] = sum_i q_t[i] k_j[i] exp(b_t[i] - b_j[i]) for j <= t; a warp per pair
+    // scores inside the chunk: A[t][u] = sum_i q_t[i] k_u[i] exp(b_t[i] - b_u[i]) for u <= t; a warp per pair
     const int warp = tid >> 5, lane = tid & 31;
-    for (int pair = warp; pair < n * n; pair += GLA_THREADS / 32) {
-        const int t = pair / n, j = pair - t * n;
-        if (j > t) continue;
+    for (int pair = warp; pair < GC * GC; pair += GLA_THREADS / 32) {
+        const int u = pair / GC, t = pair - u * GC;
         float acc = 0.f;
-        for (int i = lane; i < dk; i += 32) acc = fmaf(qs[t * dk + i] * ks[j * dk + i], expf(b[t * dk + i] - b[j * dk + i]), acc);
+        if (u <= t && t < n)
+            for (int i = lane; i < dk; i += 32) acc = fmaf(qs[t * dk + i] * ks[u * dk + i], expf(b[t * dk + i] - b[u * dk + i]), acc);
         acc = warp_sum(acc);
-        if (lane == 0) A[t * GC + j] = acc;
+        if (lane == 0) AT[pair] = acc;
     }
-    // the carried part reads q_t * exp(b_t)
+    for (int e = tid; e < GC * dk; e += GLA_THREADS) {
+        const int i = e / GC, t = e - i * GC;
+        qd[e] = t < n ? qs[t * dk + i] * expf(b[t * dk + i]) : 0.f;
+    }
     __syncthreads();
-    for (int e = tid; e < n * dk; e += GLA_THREADS) qs[e] *= expf(b[e]);
+    const int G = GLA_THREADS / dv;
+    const bool active = tid < G * dv;
+    const int j = tid % dv, g = tid / dv;
+    float acc[GC];
+#pragma unroll
+    for (int t = 0; t < GC; t++) acc[t] = 0.f;
+    if (active) {
+        const float *Pc = P + ((size_t)c * H + h) * dk * dv;
+        for (int i = g; i < dk; i += G) {
+            const float p = Pc[(size_t)i * dv + j];
+            const float4 *q4 = (const float4 *)(qd + i * GC);
+#pragma unroll
+            for (int t4 = 0; t4 < GC / 4; t4++) {
+                const float4 w = q4[t4];
+                acc[4 * t4] = fmaf(p, w.x, acc[4 * t4]); acc[4 * t4 + 1] = fmaf(p, w.y, acc[4 * t4 + 1]);
+                acc[4 * t4 + 2] = fmaf(p, w.z, acc[4 * t4 + 2]); acc[4 * t4 + 3] = fmaf(p, w.w, acc[4 * t4 + 3]);
+            }
+        }
+        for (int u = g; u < n; u += G) {
+            const float vv = proj[(size_t)(r0 + u) * ld + (size_t)2 * H * dk + (size_t)h * dv + j];
+            const float4 *a4 = (const float4 *)(AT + u * GC);
+#pragma unroll
+            for (int t4 = 0; t4 < GC / 4; t4++) {
+                const float4 w = a4[t4];
+                acc[4 * t4] = fmaf(vv, w.x, acc[4 * t4]); acc[4 * t4 + 1] = fmaf(vv, w.y, acc[4 * t4 + 1]);
+                acc[4 * t4 + 2] = fmaf(vv, w.z, acc[4 * t4 + 2]); acc[4 * t4 + 3] = fmaf(vv, w.w, acc[4 * t4 + 3]);
+            }
+        }
+#pragma unroll
+        for (int t = 0; t < GC; t++) part[t * GLA_THREADS + tid] = acc[t];      // [t][g][j]
+    }
     __syncthreads();
-    const float *Pc = P + ((size_t)c * H + h) * dk * dv;
+    // column j's outputs, groups added in order; then the unit norm over the head's values, a warp per token
     for (int e = tid; e < n * dv; e += GLA_THREADS) {
-        const int t = e / dv, j = e - t * dv;
-        float acc = 0.f;
-        for (int i = 0; i < dk; i++) acc = fmaf(Pc[(size_t)i * dv + j], qs[t * dk + i], acc);
-        for (int u = 0; u <= t; u++) acc = fmaf(A[t * GC + u], vs[u * dv + j], acc);
-        os[e] = acc;
+        const int t = e / dv, jj = e - t * dv;
+        float o = 0.f;
+        for (int gg = 0; gg < G; gg++) o += part[t * GLA_THREADS + gg * dv + jj];
+        os[e] = o;
     }
     __syncthreads();
     for (int t = warp; t < n; t += GLA_THREADS / 32) {
         float ss = 0.f;
-        for (int j = lane; j < dv; j += 32) ss = fmaf(os[t * dv + j], os[t * dv + j], ss);
+        for (int jj = lane; jj < dv; jj += 32) ss = fmaf(os[t * dv + jj], os[t * dv + jj], ss);
         ss = warp_sum(ss);
         if (lane == 0) inv[t] = 1.0f / sqrtf(ss / (float)dv + eps);
     }
     __syncthreads();
     for (int e = tid; e < n * dv; e += GLA_THREADS) {
-        const int t = e / dv, j = e - t * dv;
-        const float gate = proj[(size_t)(r0 + t) * ld + (size_t)2 * H * dk + (size_t)(H + h) * dv + j];
-        out[(size_t)(r0 + t) * ldo + (size_t)h * dv + j] = from_f32<TO>(os[e] * inv[t] * norm_w[j] * gla_silu(gate));
+        const int t = e / dv, jj = e - t * dv;
+        const float gate = proj[(size_t)(r0 + t) * ld + (size_t)2 * H * dk + (size_t)(H + h) * dv + jj];
+        out[(size_t)(r0 + t) * ldo + (size_t)h * dv + jj] = from_f32<TO>(os[e] * inv[t] * norm_w[jj] * gla_silu(gate));
     }
 }
 
 static FgPerDevice g_gla_seq_setup[2], g_gla_state_setup, g_gla_out_setup[2];
 
 static size_t gla_seq_smem(int dk, int dv) { return ((size_t)dk * dv + 3 * dk + dv + (size_t)(GLA_THREADS / dv) * dv) * sizeof(float); }
-static size_t gla_state_smem(int dk, int dv) { return ((size_t)2 * GC * dk + (size_t)GC * dv) * sizeof(float); }
-static size_t gla_out_smem(int dk, int dv) { return ((size_t)3 * GC * dk + (size_t)2 * GC * dv + GC * GC + GC) * sizeof(float); }
+static size_t gla_state_smem(int dk, int dv) { (void)dv; return (size_t)2 * GC * dk * sizeof(float); }
+static size_t gla_out_smem(int dk, int dv) {
+    return ((size_t)4 * GC * dk + (size_t)GC * dv + GC * GC + (size_t)GC * GLA_THREADS + GC) * sizeof(float);
+}
 
 extern "C" int fg_gla_chunk_tokens(void) { return GC; }
 
@@ -260,7 +313,7 @@ extern "C" int fg_gla(const float *proj, int ld, const float *z, int ldz, const 
 
 // 1 if the chunked form takes these sizes
 extern "C" int fg_gla_chunked_ok(int dk, int dv) {
-    if (dk <= 0 || dv <= 0) return 0;
+    if (dk <= 0 || dv <= 0 || dv > GLA_THREADS) return 0;
     return gla_state_smem(dk, dv) <= 200 * 1024 && gla_out_smem(dk, dv) <= 200 * 1024;
 }
 

@@ -19,6 +19,7 @@
 // rotated part (in the key pool) only.  The key map is folded into the query, q_abs[h] = W_uk[h]^T q_plain[h], so that a score
 // is q_abs . c + q_rot . k_rot, and the value map is applied to the attention's output over the latents,
 // o[h] = W_uv[h] (sum_j p_j c_j): the same sums in another order, for prompts, portions and single tokens alike.
+#include <algorithm>
 #include <cmath>
 
 #include "parts.hpp"
@@ -123,9 +124,30 @@ public:
             FG_LAUNCH("mix", fg_conv_state_update, proj.ptr<float>(), (int)proj.ld, bias, taps_, (float *)io.state, b.cu_rows, b.slots, b.n_seq,
                       (int)channels(), rt.stream);
         Tensor attn = rt.arena->matrix(M, (int64_t)H_ * hdv_, rt.dtype);
-        FG_LAUNCH("core", fg_attention_generic_ext, q.data, (int)q.ld, attn.data, (int)attn.ld, rt.dtype, b.positions, b.row_seq, table,
-                  b.table_width, io.k_pool, io.v_pool, M, H_, KV_, hd_, hdv_, io.page_size, scale_, window_, 0, softcap_,
-                  sink_ ? sinks_w_.t.ptr<float>() : nullptr, 0, rt.stream);
+        const float *sinks = sink_ ? sinks_w_.t.ptr<float>() : nullptr;
+        // bfloat16 with head size 64 / 128 for keys and values alike: the tensor-core kernels (a decode step: mma.sync with the
+        // pages split over a cluster; portions: tcgen05 tiles of 128 rows, or mma.sync tiles of 64 for a few rows)
+        const bool fast = !rt.plain_kernels && rt.dtype == FG_BF16 && io.cache_dtype == FG_BF16 && (hd_ == 64 || hd_ == 128) && hdv_ == hd_ &&
+                          io.page_size == 64 && q.ld % 8 == 0 && ((uintptr_t)q.data % 16) == 0;
+        if (fast && b.single_token) {
+            int n_splits = decode_splits(rt.n_sm, b.n_seq, H_, KV_, b.table_width, hd_);
+            float *part_o = nullptr, *part_ml = nullptr;
+            if (n_splits != 1 && n_splits != 2 && n_splits != 4 && n_splits != 8) {
+                part_o = (float *)rt.arena->alloc((size_t)b.n_seq * H_ * n_splits * hd_ * sizeof(float));
+                part_ml = (float *)rt.arena->alloc((size_t)b.n_seq * H_ * n_splits * 2 * sizeof(float));
+            }
+            FG_LAUNCH("attn", fg_attention_decode_ext, q.data, (int)q.ld, attn.data, (int)attn.ld, b.positions, table, b.table_width, io.k_pool,
+                      io.v_pool, b.n_seq, H_, KV_, hd_, io.page_size, scale_, window_, 0, n_splits, part_o, part_ml, softcap_, sinks, rt.stream);
+        } else if (fast && b.max_new * (H_ / KV_) >= 64) {
+            FG_LAUNCH("attn", fg_attention_prefill_tc_ext, q.data, (int)q.ld, attn.data, (int)attn.ld, b.cu_rows, b.seq_start, table, b.table_width,
+                      io.k_pool, io.v_pool, io.n_pages, b.n_seq, b.max_new, H_, KV_, hd_, io.page_size, scale_, window_, 0, softcap_, sinks, rt.stream);
+        } else if (fast) {
+            FG_LAUNCH("attn", fg_attention_prefill_ext, q.data, (int)q.ld, attn.data, (int)attn.ld, b.cu_rows, b.seq_start, table, b.table_width,
+                      io.k_pool, io.v_pool, b.n_seq, b.max_new, H_, KV_, hd_, io.page_size, scale_, window_, 0, softcap_, sinks, rt.stream);
+        } else {
+            FG_LAUNCH("core", fg_attention_generic_ext, q.data, (int)q.ld, attn.data, (int)attn.ld, rt.dtype, b.positions, b.row_seq, table,
+                      b.table_width, io.k_pool, io.v_pool, M, H_, KV_, hd_, hdv_, io.page_size, scale_, window_, 0, softcap_, sinks, 0, rt.stream);
+        }
         DeferredNorm started;
         o_.forward(rt, attn, nullptr, residual, FG_F32, !rt.overwrite, emit_norm, &started);
         return started;
@@ -189,6 +211,8 @@ public:
         q_up_ = Linear(tensor_of(tensors, "q_up.weight"));
         k_up_ = tensor_of(tensors, "k_up.weight");
         v_up_ = tensor_of(tensors, "v_up.weight");
+        k_lin_ = Linear(k_up_);
+        v_lin_ = Linear(v_up_);
         o_ = Linear(tensor_of(tensors, "o_proj.weight"));
         qn_w_ = as_f32(tensor_of(tensors, "q_down_norm.weight"), rt.stream);
         kvn_w_ = as_f32(tensor_of(tensors, "kv_down_norm.weight"), rt.stream);
@@ -208,19 +232,64 @@ public:
         Tensor q = q_up_.forward(rt, cq, nullptr, Tensor(), FG_F32, false, nullptr, nullptr);
         FG_LAUNCH("mix", fg_latent_append, down.ptr<float>() + qr_, (int)down.ld, kvn_w_.t.ptr<float>(), eps_, cos_t, sin_t, dr_ / 2, b.positions,
                   b.row_seq, table, b.table_width, io.k_pool, io.v_pool, rt.dtype, M, r_, dr_, io.page_size, rt.stream);
-        // per head [q_abs (kv_rank) | q_rot (rot_dim)]
-        Tensor qf = rt.arena->matrix(M, (int64_t)H_ * (r_ + dr_), rt.dtype);
-        FG_LAUNCH("mix", fg_head_gemm, q.data, q.dtype, (int)q.ld, d_ + dr_, k_up_.t.data, k_up_.t.dtype, (int)k_up_.t.ld, 1, qf.data, qf.dtype,
-                  (int)qf.ld, r_ + dr_, nullptr, 0, M, r_, d_, H_, rt.stream);
-        FG_LAUNCH("mix", fg_rope_pairs, q.ptr<float>(), (int)q.ld, d_ + dr_, d_, qf.data, qf.dtype, (int)qf.ld, r_ + dr_, r_, b.positions, cos_t, sin_t,
-                  dr_ / 2, M, H_, dr_, rt.stream);
-        Tensor lat = rt.arena->matrix(M, (int64_t)H_ * r_, rt.dtype);
-        FG_LAUNCH("core", fg_attention_generic_ext, qf.data, (int)qf.ld, lat.data, (int)lat.ld, rt.dtype, b.positions, b.row_seq, table, b.table_width,
-                  io.k_pool, io.v_pool, M, H_, 1, dr_, r_, io.page_size, scale_, 0, 0, 0.f, sink_ ? sinks_w_.t.ptr<float>() : nullptr, 1, rt.stream);
         Tensor o = rt.arena->matrix(M, (int64_t)H_ * dv_, rt.dtype);
         const float *gate = gate_ ? down.ptr<float>() + qr_ + r_ + dr_ : nullptr;
-        FG_LAUNCH("mix", fg_head_gemm, lat.data, lat.dtype, (int)lat.ld, r_, v_up_.t.data, v_up_.t.dtype, (int)v_up_.t.ld, 0, o.data, o.dtype, (int)o.ld,
-                  dv_, gate, (int)down.ld, M, dv_, r_, H_, rt.stream);
+        const float *sinks = sink_ ? sinks_w_.t.ptr<float>() : nullptr;
+        const int HQ = d_ + dr_;
+        // A step of whole prompts in bfloat16 whose head sizes the tensor-core kernels take: ordinary multi-head attention over
+        // keys and values expanded for the step's tokens (nothing older is in the cache), in pools of the step's own.
+        bool whole_prompts = !b.single_token && !b.host_seq_start.empty() && !rt.plain_kernels && rt.dtype == FG_BF16 && (HQ == 64 || HQ == 128) &&
+                             dv_ <= HQ && io.page_size == 64 && b.n_seq <= 1024 && k_up_.t.dtype == FG_BF16 && v_up_.t.dtype == FG_BF16;
+        for (size_t s = 0; whole_prompts && s < b.host_seq_start.size(); s++) whole_prompts = b.host_seq_start[s] == 0;
+        if (whole_prompts) {
+            const int P = io.page_size;
+            int n_pages = 0, width = 1;
+            for (int s = 0; s < b.n_seq; s++) {
+                const int n = (b.host_cu_rows[(size_t)s + 1] - b.host_cu_rows[(size_t)s] + P - 1) / P;
+                n_pages += n;
+                width = std::max(width, n);
+            }
+            Tensor cn = rt.arena->matrix(M, r_, FG_BF16);
+            FG_LAUNCH("mix", fg_rmsnorm_strided, down.ptr<float>() + qr_, (int)down.ld, kvn_w_.t.ptr<float>(), cn.data, cn.dtype, (int)cn.ld, M, r_, eps_, rt.stream);
+            Tensor kp = k_lin_.forward(rt, cn, nullptr, Tensor(), FG_BF16, false, nullptr, nullptr);
+            Tensor vp = v_lin_.forward(rt, cn, nullptr, Tensor(), FG_BF16, false, nullptr, nullptr);
+            int *tmp_table = (int *)rt.arena->alloc((size_t)b.n_seq * width * sizeof(int));
+            const size_t pool_elems = (size_t)n_pages * H_ * P * HQ;
+            Tensor qx = rt.arena->matrix(M, (int64_t)H_ * HQ, FG_BF16), ox = rt.arena->matrix(M, (int64_t)H_ * HQ, FG_BF16);
+            void *Kx = rt.arena->alloc(pool_elems * 2), *Vx = rt.arena->alloc(pool_elems * 2);
+            FG_LAUNCH("mix", fg_seq_page_table, b.cu_rows, b.n_seq, width, P, tmp_table, rt.stream);
+            FG_LAUNCH("mix", fg_latent_expand, q.ptr<float>(), (int)q.ld, down.ptr<float>(), (int)down.ld, qr_ + r_, kp.data, (int)kp.ld, vp.data, (int)vp.ld,
+                      cos_t, sin_t, dr_ / 2, b.positions, b.row_seq, tmp_table, width, qx.data, Kx, Vx, M, H_, d_, dr_, dv_, P, rt.stream);
+            if (b.max_new >= 64)
+                FG_LAUNCH("attn", fg_attention_prefill_tc_ext, qx.data, (int)qx.ld, ox.data, (int)ox.ld, b.cu_rows, b.seq_start, tmp_table, width, Kx, Vx,
+                          n_pages, b.n_seq, b.max_new, H_, H_, HQ, P, scale_, 0, 0, 0.f, sinks, rt.stream);
+            else
+                FG_LAUNCH("attn", fg_attention_prefill_ext, qx.data, (int)qx.ld, ox.data, (int)ox.ld, b.cu_rows, b.seq_start, tmp_table, width, Kx, Vx,
+                          b.n_seq, b.max_new, H_, H_, HQ, P, scale_, 0, 0, 0.f, sinks, rt.stream);
+            FG_LAUNCH("mix", fg_gate_slice, ox.data, (int)ox.ld, HQ, gate, (int)down.ld, o.data, (int)o.ld, o.dtype, M, H_, dv_, rt.stream);
+        } else {
+            // per head [q_abs (kv_rank) | q_rot (rot_dim)]
+            Tensor qf = rt.arena->matrix(M, (int64_t)H_ * (r_ + dr_), rt.dtype);
+            FG_LAUNCH("mix", fg_head_gemm, q.data, q.dtype, (int)q.ld, d_ + dr_, k_up_.t.data, k_up_.t.dtype, (int)k_up_.t.ld, 1, qf.data, qf.dtype,
+                      (int)qf.ld, r_ + dr_, nullptr, 0, M, r_, d_, H_, rt.stream);
+            FG_LAUNCH("mix", fg_rope_pairs, q.ptr<float>(), (int)q.ld, d_ + dr_, d_, qf.data, qf.dtype, (int)qf.ld, r_ + dr_, r_, b.positions, cos_t, sin_t,
+                      dr_ / 2, M, H_, dr_, rt.stream);
+            Tensor lat = rt.arena->matrix(M, (int64_t)H_ * r_, rt.dtype);
+            if (b.single_token && dr_ <= 128 && dr_ % 4 == 0 && r_ % 4 == 0 && M <= 65535) {
+                // a block per (row, 8 heads, split of the keys): enough blocks to fill the GPU, at least 8 keys a warp
+                const int blocks = M * ((H_ + 7) / 8);
+                int n_splits = std::max(1, std::min({(rt.n_sm + blocks - 1) / blocks, 16, (b.max_len + 63) / 64}));
+                const long long floats = FG_KERNEL("mix", fg_latent_decode_scratch_floats)(M, H_, r_, n_splits);
+                float *part = floats > 0 ? (float *)rt.arena->alloc((size_t)floats * sizeof(float)) : nullptr;
+                FG_LAUNCH("mix", fg_latent_decode, qf.data, (int)qf.ld, lat.data, (int)lat.ld, rt.dtype, b.positions, b.row_seq, table, b.table_width,
+                          io.k_pool, io.v_pool, M, H_, r_, dr_, io.page_size, scale_, sinks, n_splits, part, rt.stream);
+            } else {
+                FG_LAUNCH("core", fg_attention_generic_ext, qf.data, (int)qf.ld, lat.data, (int)lat.ld, rt.dtype, b.positions, b.row_seq, table, b.table_width,
+                          io.k_pool, io.v_pool, M, H_, 1, dr_, r_, io.page_size, scale_, 0, 0, 0.f, sinks, 1, rt.stream);
+            }
+            FG_LAUNCH("mix", fg_head_gemm, lat.data, lat.dtype, (int)lat.ld, r_, v_up_.t.data, v_up_.t.dtype, (int)v_up_.t.ld, 0, o.data, o.dtype, (int)o.ld,
+                      dv_, gate, (int)down.ld, M, dv_, r_, H_, rt.stream);
+        }
         DeferredNorm started;
         o_.forward(rt, o, nullptr, residual, FG_F32, !rt.overwrite, emit_norm, &started);
         return started;
@@ -231,7 +300,7 @@ private:
     float scale_ = 1.f, eps_ = 1e-6f;
     bool sink_ = false, gate_ = false;
     PositionEncoding *position_ = nullptr;
-    Linear down_, q_up_, o_;
+    Linear down_, q_up_, o_, k_lin_, v_lin_;
     Weight k_up_, v_up_, qn_w_, kvn_w_, sinks_w_;
 };
 
