@@ -156,8 +156,8 @@ def salulorn_config(width, heads, kv_heads, head_dim, ff, vocab, window, expert_
     g = {"heads": width // 128, "dim": 64, "vdim": 128, "tau": 16.0, "decay_rank": 16}
     att = {"heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim, "scale": head_dim ** -0.5, "conv": 4,
            "mask": {"size": window}, "rot": {"base": 1000000.0, "dims": head_dim}, "softcap": 50.0}
-    lat = {"heads": heads, "dim": head_dim, "rot_dim": 64, "vdim": head_dim, "kv_rank": 512, "q_rank": width * 3 // 4,
-           "scale": (head_dim + 64) ** -0.5,
+    lat = {"heads": heads, "dim": 64, "rot_dim": 64, "vdim": head_dim, "kv_rank": 512, "q_rank": width * 3 // 4,
+           "scale": 128 ** -0.5,
            "rot": {"base": 10000.0, "dims": 64, "scaling": {"factor": 40.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
     dense = {"kind": "dense", "ff": ff}
     layers = []

@@ -162,6 +162,137 @@ latent_decode_kernel(const T *__restrict__ q, int ldq, T *__restrict__ out, int 
     }
 }
 
+// ---------------------------------------------------------------------------------------------- the same on the tensor cores
+// bfloat16, pages of 64 positions, R a multiple of 64, DR a multiple of 16.  One block per (row, 16 heads, split of the
+// PAGES); per page: (1) S = Q K^T, warp w the page's keys 8 w .. 8 w + 7 as m16n8k16 MMAs whose B operand - a key's numbers
+// along k - is read straight from the cache rows; (2) the scores meet in shared memory, warp w runs the online softmax of
+// rows 2 w and 2 w + 1 (running maximum and sum per row in shared memory) and leaves bfloat16 weights there; (3) O += P V,
+// warp w the latent's columns w R / 8 .. , the B operand - two keys of one column - packed from 16-bit reads of the cache rows.
+#define LM_WARPS 8
+#define LM_HEADS 16
+__device__ __forceinline__ void lat_mma(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <int NT>                     // n-tiles of 8 latent columns a warp owns: R = 64 NT
+__global__ void __launch_bounds__(LM_WARPS * 32)
+latent_decode_mma_kernel(const bf16 *__restrict__ q, int ldq, bf16 *__restrict__ out, int ldo, const int *__restrict__ positions,
+                         const int *__restrict__ row_seq, const int *__restrict__ block_table, int table_width, const bf16 *__restrict__ k_pool,
+                         const bf16 *__restrict__ v_pool, int H, int DR, float scale_log2, const float *__restrict__ sinks, int n_splits,
+                         float *__restrict__ part) {
+    constexpr int R = 64 * NT, PG = 64;
+    extern __shared__ __align__(16) uint8_t lm_smem[];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, r = lane >> 2, cp = (lane & 3) * 2;
+    const int m_row = blockIdx.y, h0 = blockIdx.x * LM_HEADS, split = blockIdx.z;
+    const int nh = min(LM_HEADS, H - h0);
+    const int QD = R + DR, QS = QD + 8, PS = PG + 8;
+    bf16 *Qs = (bf16 *)lm_smem;                                   // [16][QS]
+    bf16 *Ps = Qs + LM_HEADS * QS;                                // [16][PS]
+    float *Ss = (float *)(Ps + LM_HEADS * PS);                    // [16][PG + 1]
+    float *m_s = Ss + LM_HEADS * (PG + 1), *l_s = m_s + LM_HEADS, *corr_s = l_s + LM_HEADS;
+    const int pos = positions[m_row];
+    const int *bt = block_table + (size_t)row_seq[m_row] * table_width;
+    for (int e = threadIdx.x; e < LM_HEADS * QD; e += LM_WARPS * 32) {
+        const int hh = e / QD, d = e - hh * QD;
+        Qs[hh * QS + d] = hh < nh ? q[(size_t)m_row * ldq + (size_t)(h0 + hh) * QD + d] : __float2bfloat16_rn(0.f);
+    }
+    if (threadIdx.x < LM_HEADS) {
+        const bool sink = sinks && split == 0 && threadIdx.x < nh;
+        m_s[threadIdx.x] = sink ? sinks[h0 + threadIdx.x] * 1.4426950408889634f : -INFINITY;
+        l_s[threadIdx.x] = sink ? 1.f : 0.f;
+    }
+    __syncthreads();
+    float o[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f;
+    const int last_page = pos / PG;
+    for (int pg = split; pg <= last_page; pg += n_splits) {
+        const size_t base = (size_t)bt[pg] * PG;
+        // (1) scores of this warp's eight keys
+        {
+            const size_t at = base + 8 * warp + r;
+            const bf16 *lat = v_pool + at * R, *rot = k_pool + at * DR;
+            float c[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+            for (int kc = 0; kc < QD; kc += 16) {
+                const bf16 *qa = Qs + r * QS + kc + cp;
+                const uint32_t a0 = *(const uint32_t *)qa, a1 = *(const uint32_t *)(qa + 8 * QS), a2 = *(const uint32_t *)(qa + 8),
+                               a3 = *(const uint32_t *)(qa + 8 * QS + 8);
+                const bf16 *kb = (kc < R ? lat + kc : rot + (kc - R)) + cp;
+                lat_mma(c, a0, a1, a2, a3, *(const uint32_t *)kb, *(const uint32_t *)(kb + 8));
+            }
+            const int col = 8 * warp + cp, key = pg * PG + col;
+            Ss[r * (PG + 1) + col] = key <= pos ? c[0] * scale_log2 : -INFINITY;
+            Ss[r * (PG + 1) + col + 1] = key + 1 <= pos ? c[1] * scale_log2 : -INFINITY;
+            Ss[(r + 8) * (PG + 1) + col] = key <= pos ? c[2] * scale_log2 : -INFINITY;
+            Ss[(r + 8) * (PG + 1) + col + 1] = key + 1 <= pos ? c[3] * scale_log2 : -INFINITY;
+        }
+        __syncthreads();
+        // (2) online softmax of rows 2 warp, 2 warp + 1
+#pragma unroll
+        for (int k = 0; k < 2; k++) {
+            const int row = 2 * warp + k;
+            const float v0 = Ss[row * (PG + 1) + lane], v1 = Ss[row * (PG + 1) + lane + 32];
+            const float m_old = m_s[row], m_new = fmaxf(m_old, warp_max(fmaxf(v0, v1)));
+            const float p0 = m_new == -INFINITY ? 0.f : lat_ex2(v0 - m_new), p1 = m_new == -INFINITY ? 0.f : lat_ex2(v1 - m_new);
+            const float sum = warp_sum(p0 + p1);
+            Ps[row * PS + lane] = __float2bfloat16_rn(p0);
+            Ps[row * PS + lane + 32] = __float2bfloat16_rn(p1);
+            __syncwarp();
+            if (lane == 0) {
+                const float corr = m_old == -INFINITY ? 0.f : lat_ex2(m_old - m_new);
+                corr_s[row] = corr;
+                l_s[row] = l_s[row] * corr + sum;
+                m_s[row] = m_new;
+            }
+        }
+        __syncthreads();
+        // (3) O += P V on this warp's columns
+        {
+            const float c0 = corr_s[r], c1 = corr_s[r + 8];
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) { o[nt][0] *= c0; o[nt][1] *= c0; o[nt][2] *= c1; o[nt][3] *= c1; }
+            const unsigned short *V = (const unsigned short *)(v_pool + base * R);
+#pragma unroll
+            for (int ks = 0; ks < PG; ks += 16) {
+                const bf16 *pa = Ps + r * PS + ks + cp;
+                const uint32_t a0 = *(const uint32_t *)pa, a1 = *(const uint32_t *)(pa + 8 * PS), a2 = *(const uint32_t *)(pa + 8),
+                               a3 = *(const uint32_t *)(pa + 8 * PS + 8);
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++) {
+                    const unsigned short *vb = V + (size_t)(ks + cp) * R + warp * (R / 8) + nt * 8 + r;
+                    const uint32_t b0 = (uint32_t)vb[0] | ((uint32_t)vb[R] << 16), b1 = (uint32_t)vb[8 * R] | ((uint32_t)vb[9 * R] << 16);
+                    lat_mma(o[nt], a0, a1, a2, a3, b0, b1);
+                }
+            }
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < 2; k++) {
+        const int row = r + 8 * k;
+        if (row >= nh) continue;
+        const float M = m_s[row], L = l_s[row];
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) {
+            const int col = warp * (R / 8) + nt * 8 + cp;
+            const float x0 = o[nt][2 * k], x1 = o[nt][2 * k + 1];
+            if (n_splits == 1) {
+                const float inv = L > 0.f ? 1.0f / L : 0.f;
+                __nv_bfloat162 t = __floats2bfloat162_rn(x0 * inv, x1 * inv);
+                *(uint32_t *)(out + (size_t)m_row * ldo + (size_t)(h0 + row) * R + col) = *(uint32_t *)&t;
+            } else {
+                float *pr = part + (((size_t)m_row * H + h0 + row) * n_splits + split) * (R + 2);
+                pr[col] = x0; pr[col + 1] = x1;
+                if (warp == 0 && nt == 0 && cp == 0) { pr[R] = M; pr[R + 1] = L; }
+            }
+        }
+    }
+}
+
 template <typename T>
 __global__ void latent_merge_kernel(const float *__restrict__ part, T *__restrict__ out, int ldo, int H, int R, int n_splits) {
     pdl_launch_dependents();
@@ -293,6 +424,37 @@ extern "C" int fg_latent_decode(const void *q, int ldq, void *out, int ldo, int 
 #undef LAT_BY_SIZE
 #undef LAT_RUN
     return FG_ERR_BAD_DTYPE;
+}
+
+static size_t latent_mma_smem(int R, int DR) {
+    return (size_t)LM_HEADS * (R + DR + 8) * 2 + (size_t)LM_HEADS * (64 + 8) * 2 + (size_t)LM_HEADS * 65 * 4 + 3 * LM_HEADS * 4;
+}
+
+// 1 if the tensor-core form takes these sizes (bfloat16 only)
+extern "C" int fg_latent_decode_mma_ok(int R, int DR, int page_size) { return page_size == 64 && R % 64 == 0 && R >= 64 && R <= 512 && DR % 16 == 0 && DR > 0; }
+
+// q: [M, H * (R + DR)], out: [M, H * R] bfloat16; n_splits over the PAGES of a sequence; part as for fg_latent_decode
+extern "C" int fg_latent_decode_mma(const void *q, int ldq, void *out, int ldo, const int *positions, const int *row_seq,
+                                    const int *block_table, int table_width, const void *k_pool, const void *v_pool, int M, int H, int R,
+                                    int DR, int page_size, float scale, const float *sinks, int n_splits, float *part, cudaStream_t stream) {
+    if (M <= 0) return 0;
+    if (!fg_latent_decode_mma_ok(R, DR, page_size) || H <= 0 || n_splits < 1 || M > 65535 || n_splits > 65535) return FG_ERR_BAD_SIZE;
+    if ((n_splits > 1 && !part) || ldq % 2 || ldo % 2 || ((uintptr_t)q & 3) || ((uintptr_t)out & 3) || ((uintptr_t)k_pool & 3) || ((uintptr_t)v_pool & 3))
+        return FG_ERR_BAD_SIZE;
+    const size_t smem = latent_mma_smem(R, DR);
+    const dim3 grid((H + LM_HEADS - 1) / LM_HEADS, M, n_splits);
+    const float scale_log2 = scale * 1.4426950408889634f;
+    int code = FG_ERR_BAD_SIZE;
+#define LM_RUN(NT) code = fg_launch(latent_decode_mma_kernel<NT>, grid, dim3(LM_WARPS * 32), smem, stream, (const bf16 *)q, ldq, (bf16 *)out, ldo, \
+                                    positions, row_seq, block_table, table_width, (const bf16 *)k_pool, (const bf16 *)v_pool, H, DR, scale_log2, sinks, \
+                                    n_splits, part)
+    switch (R / 64) {
+        case 1: LM_RUN(1); break; case 2: LM_RUN(2); break; case 3: LM_RUN(3); break; case 4: LM_RUN(4); break;
+        case 5: LM_RUN(5); break; case 6: LM_RUN(6); break; case 7: LM_RUN(7); break; case 8: LM_RUN(8); break;
+    }
+#undef LM_RUN
+    if (code || n_splits == 1) return code;
+    return fg_launch(latent_merge_kernel<bf16>, dim3(H, M), dim3(128), 0, stream, (const float *)part, (bf16 *)out, ldo, H, R, n_splits);
 }
 
 extern "C" int fg_seq_page_table(const int *cu_rows, int n_seq, int width, int page_size, int *table, cudaStream_t stream) {

@@ -103,8 +103,13 @@ __device__ __forceinline__ float ex2(float x) {
 // cap_log2 * tanh(raw * cap_in) with cap_log2 = cap * log2(e) and cap_in = scale / cap.
 // A sink (a key without a value that joins the denominator once) needs nothing here: the caller starts ONE of the running
 // (m, l) pairs that are merged into a row's result at (sink * log2(e), 1) instead of (-inf, 0).
-// tanh(x) = 1 - 2 / (1 + 2^(2 x log2(e))): two special-function instructions, absolute error about 2e-7
-__device__ __forceinline__ float tanh_fast(float x) { return 1.0f - __fdividef(2.0f, 1.0f + ex2(x * (2.0f * 1.4426950408889634f))); }
+// tanh.approx: one special-function instruction, relative error 2^-11 - the size of the rounding that the bfloat16 operands
+// of q . k have already put into the score it caps
+__device__ __forceinline__ float tanh_fast(float x) {
+    float y;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 
 template <int NO, bool MASK>
 __device__ __forceinline__ void softmax_update(float (&s)[8][4], float (&o)[NO][4], float (&m)[2], float (&l)[2],

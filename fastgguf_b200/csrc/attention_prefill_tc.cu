@@ -167,8 +167,13 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
     asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
     return r;
 }
-// tanh(x) = 1 - 2 / (1 + 2^(2 x log2(e))): two special-function instructions, absolute error about 2e-7
-__device__ __forceinline__ float tanh_fast(float x) { return 1.0f - __fdividef(2.0f, 1.0f + ex2(x * (2.0f * 1.4426950408889634f))); }
+// tanh.approx: one special-function instruction, relative error 2^-11 - the size of the rounding that the bfloat16 operands
+// of q . k have already put into the score it caps
+__device__ __forceinline__ float tanh_fast(float x) {
+    float y;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 // CAP: capped scores, cap * tanh(scale * raw / cap); in the base-2 domain cap_log2 * tanh(raw * cap_in) with
 // cap_log2 = cap * log2(e) (passed as `scale`) and cap_in = scale / cap.  tanh keeps the order of the raw scores, so the
 // largest raw score still names the largest capped one.

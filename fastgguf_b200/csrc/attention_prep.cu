@@ -246,21 +246,34 @@ head_gemv_kernel(const void *__restrict__ A, int a_dtype, int lda, int a_stride,
     if (TRANSPOSED) {
         n = blockIdx.x * 256 + threadIdx.x;
         if (n >= N) return;
-        for (int k = 0; k < K; k++) {
-            const float w = load_as(W, w_dtype, ((size_t)h * K + k) * ldw + n);
+        // eight weights are on their way before the first of them is used
+        for (int k0 = 0; k0 < K; k0 += 8) {
+            float w[8];
 #pragma unroll
-            for (int m = 0; m < HV_ROWS; m++)
-                if (m < M) acc[m] = fmaf(as[m * K + k], w, acc[m]);
+            for (int u = 0; u < 8; u++) w[u] = k0 + u < K ? load_as(W, w_dtype, ((size_t)h * K + k0 + u) * ldw + n) : 0.f;
+#pragma unroll
+            for (int u = 0; u < 8; u++) {
+                if (k0 + u >= K) break;
+#pragma unroll
+                for (int m = 0; m < HV_ROWS; m++)
+                    if (m < M) acc[m] = fmaf(as[m * K + k0 + u], w[u], acc[m]);
+            }
         }
     } else {
         const int lane = threadIdx.x & 31;
         n = blockIdx.x * 8 + (threadIdx.x >> 5);
         if (n >= N) return;
-        for (int k = lane; k < K; k += 32) {
-            const float w = load_as(W, w_dtype, ((size_t)h * N + n) * ldw + k);
+        for (int k0 = lane; k0 < K; k0 += 128) {
+            float w[4];
 #pragma unroll
-            for (int m = 0; m < HV_ROWS; m++)
-                if (m < M) acc[m] = fmaf(as[m * K + k], w, acc[m]);
+            for (int u = 0; u < 4; u++) w[u] = k0 + 32 * u < K ? load_as(W, w_dtype, ((size_t)h * N + n) * ldw + k0 + 32 * u) : 0.f;
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                if (k0 + 32 * u >= K) break;
+#pragma unroll
+                for (int m = 0; m < HV_ROWS; m++)
+                    if (m < M) acc[m] = fmaf(as[m * K + k0 + 32 * u], w[u], acc[m]);
+            }
         }
 #pragma unroll
         for (int m = 0; m < HV_ROWS; m++)

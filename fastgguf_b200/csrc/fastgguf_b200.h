@@ -112,6 +112,10 @@ long long fg_latent_decode_scratch_floats(int M, int H, int R, int n_splits);
 int fg_latent_decode(const void *q, int ldq, void *out, int ldo, int dtype, const int *positions, const int *row_seq,
                      const int *block_table, int table_width, const void *k_pool, const void *v_pool, int M, int H, int R,
                      int DR, int page_size, float scale, const float *sinks, int n_splits, float *part, cudaStream_t stream);
+int fg_latent_decode_mma_ok(int R, int DR, int page_size);
+int fg_latent_decode_mma(const void *q, int ldq, void *out, int ldo, const int *positions, const int *row_seq,
+                         const int *block_table, int table_width, const void *k_pool, const void *v_pool, int M, int H, int R,
+                         int DR, int page_size, float scale, const float *sinks, int n_splits, float *part, cudaStream_t stream);
 int fg_seq_page_table(const int *cu_rows, int n_seq, int width, int page_size, int *table, cudaStream_t stream);
 int fg_latent_expand(const float *q, int ldq, const float *kv, int ldkv, int rot_at, const void *kp, int ldkp, const void *vp,
                      int ldvp, const float *cos_t, const float *sin_t, int tbl_half, const int *positions, const int *row_seq,

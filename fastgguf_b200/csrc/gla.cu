@@ -100,15 +100,22 @@ __global__ void gla_chunk_plan_kernel(const int *__restrict__ cu_rows, int n_seq
     }
 }
 
-// b[t][i] = sum_(s <= t) log a_s[i] for the chunk's tokens, into shared memory (row stride dk); one thread a channel
+// b[t][i] = sum_(s <= t) log a_s[i] for the chunk's tokens, into shared memory (row stride dk); one thread a channel.  The
+// chunk's logits are all requested before the first is used (a load per step of the running sum would wait for memory GC times).
 __device__ __forceinline__ void gla_cumulative_log_decay(const float *__restrict__ z, int ldz, const float *__restrict__ z_bias, int r0, int n,
                                                          int h, int dk, float inv_tau, float *b, int tid) {
     for (int i = tid; i < dk; i += GLA_THREADS) {
         const float bias = z_bias[(size_t)h * dk + i];
+        float zz[GC];
+#pragma unroll
+        for (int t = 0; t < GC; t++) zz[t] = t < n ? z[(size_t)(r0 + t) * ldz + (size_t)h * dk + i] : 0.f;
         float run = 0.f;
-        for (int t = 0; t < n; t++) {
-            run += log_sigmoid(z[(size_t)(r0 + t) * ldz + (size_t)h * dk + i] + bias) * inv_tau;
-            b[t * dk + i] = run;
+#pragma unroll
+        for (int t = 0; t < GC; t++) {
+            if (t < n) {
+                run += log_sigmoid(zz[t] + bias) * inv_tau;
+                b[t * dk + i] = run;
+            }
         }
     }
 }
@@ -217,7 +224,7 @@ gla_chunk_out_kernel(const float *__restrict__ proj, int ld, const float *__rest
         const int u = pair / GC, t = pair - u * GC;
         float acc = 0.f;
         if (u <= t && t < n)
-            for (int i = lane; i < dk; i += 32) acc = fmaf(qs[t * dk + i] * ks[u * dk + i], expf(b[t * dk + i] - b[u * dk + i]), acc);
+            for (int i = lane; i < dk; i += 32) acc = fmaf(qs[t * dk + i] * ks[u * dk + i], __expf(b[t * dk + i] - b[u * dk + i]), acc);
         acc = warp_sum(acc);
         if (lane == 0) AT[pair] = acc;
     }
@@ -234,18 +241,33 @@ gla_chunk_out_kernel(const float *__restrict__ proj, int ld, const float *__rest
     for (int t = 0; t < GC; t++) acc[t] = 0.f;
     if (active) {
         const float *Pc = P + ((size_t)c * H + h) * dk * dv;
-        for (int i = g; i < dk; i += G) {
-            const float p = Pc[(size_t)i * dv + j];
-            const float4 *q4 = (const float4 *)(qd + i * GC);
+        // eight rows of the state are requested before the first is used
+        for (int i0 = g; i0 < dk; i0 += 8 * G) {
+            float p8[8];
 #pragma unroll
-            for (int t4 = 0; t4 < GC / 4; t4++) {
-                const float4 w = q4[t4];
-                acc[4 * t4] = fmaf(p, w.x, acc[4 * t4]); acc[4 * t4 + 1] = fmaf(p, w.y, acc[4 * t4 + 1]);
-                acc[4 * t4 + 2] = fmaf(p, w.z, acc[4 * t4 + 2]); acc[4 * t4 + 3] = fmaf(p, w.w, acc[4 * t4 + 3]);
+            for (int k = 0; k < 8; k++) p8[k] = i0 + k * G < dk ? Pc[(size_t)(i0 + k * G) * dv + j] : 0.f;
+#pragma unroll
+            for (int k = 0; k < 8; k++) {
+                const int i = i0 + k * G;
+                if (i >= dk) break;
+                const float p = p8[k];
+                const float4 *q4 = (const float4 *)(qd + i * GC);
+#pragma unroll
+                for (int t4 = 0; t4 < GC / 4; t4++) {
+                    const float4 w = q4[t4];
+                    acc[4 * t4] = fmaf(p, w.x, acc[4 * t4]); acc[4 * t4 + 1] = fmaf(p, w.y, acc[4 * t4 + 1]);
+                    acc[4 * t4 + 2] = fmaf(p, w.z, acc[4 * t4 + 2]); acc[4 * t4 + 3] = fmaf(p, w.w, acc[4 * t4 + 3]);
+                }
             }
         }
-        for (int u = g; u < n; u += G) {
-            const float vv = proj[(size_t)(r0 + u) * ld + (size_t)2 * H * dk + (size_t)h * dv + j];
+        float vu[GC];                                           // this group's values of column j, requested together
+#pragma unroll
+        for (int k = 0; k < GC; k++) vu[k] = (g + k * G < n) ? proj[(size_t)(r0 + g + k * G) * ld + (size_t)2 * H * dk + (size_t)h * dv + j] : 0.f;
+#pragma unroll
+        for (int k = 0; k < GC; k++) {
+            const int u = g + k * G;
+            if (u >= n) break;
+            const float vv = vu[k];
             const float4 *a4 = (const float4 *)(AT + u * GC);
 #pragma unroll
             for (int t4 = 0; t4 < GC / 4; t4++) {

@@ -275,7 +275,16 @@ public:
             FG_LAUNCH("mix", fg_rope_pairs, q.ptr<float>(), (int)q.ld, d_ + dr_, d_, qf.data, qf.dtype, (int)qf.ld, r_ + dr_, r_, b.positions, cos_t, sin_t,
                       dr_ / 2, M, H_, dr_, rt.stream);
             Tensor lat = rt.arena->matrix(M, (int64_t)H_ * r_, rt.dtype);
-            if (b.single_token && dr_ <= 128 && dr_ % 4 == 0 && r_ % 4 == 0 && M <= 65535) {
+            if (b.single_token && M <= 65535 && !rt.plain_kernels && rt.dtype == FG_BF16 && io.cache_dtype == FG_BF16 &&
+                FG_KERNEL("mix", fg_latent_decode_mma_ok)(r_, dr_, io.page_size)) {
+                // tensor cores: a block per (row, 16 heads, split of the pages), enough blocks to fill the GPU
+                const int blocks = M * ((H_ + 15) / 16), pages = b.max_len / io.page_size + 1;
+                int n_splits = std::max(1, std::min({(rt.n_sm + blocks - 1) / blocks, 32, pages}));
+                const long long floats = FG_KERNEL("mix", fg_latent_decode_scratch_floats)(M, H_, r_, n_splits);
+                float *part = floats > 0 ? (float *)rt.arena->alloc((size_t)floats * sizeof(float)) : nullptr;
+                FG_LAUNCH("mix", fg_latent_decode_mma, qf.data, (int)qf.ld, lat.data, (int)lat.ld, b.positions, b.row_seq, table, b.table_width, io.k_pool,
+                          io.v_pool, M, H_, r_, dr_, io.page_size, scale_, sinks, n_splits, part, rt.stream);
+            } else if (b.single_token && dr_ <= 128 && dr_ % 4 == 0 && r_ % 4 == 0 && M <= 65535) {
                 // a block per (row, 8 heads, split of the keys): enough blocks to fill the GPU, at least 8 keys a warp
                 const int blocks = M * ((H_ + 7) / 8);
                 int n_splits = std::max(1, std::min({(rt.n_sm + blocks - 1) / blocks, 16, (b.max_len + 63) / 64}));

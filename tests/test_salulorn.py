@@ -14,8 +14,9 @@ from salulorn_cases import CASES, attention, config, dense, gla, latent, make_mo
 
 pytestmark = pytest.mark.gpu
 
-#: max |dlogit| / max |logit| against the float64 plain implementation; a key wrongly seen or a lost state is at 1e-3 and above
-TOL = {"float32": 2e-5, "bfloat16": 6e-2}
+#: max |dlogit| / max |logit| against the float64 plain implementation.  float32: a key wrongly seen or a lost state is at 1e-3
+#: and above.  bfloat16 with sharpened attention and looped layers: rounding reaches 6e-2, a structural fault 0.3 and more
+TOL = {"float32": 2e-5, "bfloat16": 1e-1}
 
 
 def tokens_for(case, n, seed):
@@ -98,6 +99,9 @@ MIXERS = {
     "long attention, window past a page, head 64": attention(4, 2, 64, 64, 0.125, conv=3, size=70, rot=(250000.0, 64), softcap=30.0),
     "long attention, window of a page, keys 128 and values 64": attention(2, 1, 128, 64, 0.09, size=64, rot=(1000.0, 32)),
     "long latent attention, wide latent": latent(4, 64, 32, 64, 160, 96, 0.1, 10000.0, scaling=(16.0, 128, 32.0, 1.0)),
+    # a latent of a multiple of 64 numbers: decode steps on the tensor cores; 20 heads are a group of 16 and one of 4
+    "long latent attention, latent of 128, twenty heads": latent(20, 32, 32, 48, 128, 64, 0.12, 10000.0),
+    "long latent attention, latent of 64, heads of 128 for whole prompts": latent(3, 96, 32, 128, 64, 80, 0.09, 50000.0, scaling=(4.0, 64, 8.0, 1.0)),
 }
 
 
