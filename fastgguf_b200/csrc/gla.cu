@@ -135,11 +135,11 @@ gla_chunk_state_kernel(const float *__restrict__ proj, int ld, const float *__re
     float *b = sm, *kd = b + GC * dk;                          // b: [GC][dk]; kd: [dk][GC], zero beyond the chunk's n tokens
     gla_cumulative_log_decay(z, ldz, z_bias, r0, n, h, dk, inv_tau, b, tid);
     __syncthreads();
-    for (int e = tid; e < GC * dk; e += GLA_THREADS) {
-        const int i = e / GC, t = e - i * GC;
-        kd[e] = t < n ? proj[(size_t)(r0 + t) * ld + (size_t)(H + h) * dk + i] * expf(b[(n - 1) * dk + i] - b[t * dk + i]) : 0.f;
-    }
-    for (int i = tid; i < dk; i += GLA_THREADS) D[((size_t)c * H + h) * dk + i] = expf(b[(n - 1) * dk + i]);
+    // (loops over a [token][channel] tile walk tokens by warp and channels by lane: no division by a run-time size)
+    for (int t = tid >> 5; t < GC; t += GLA_THREADS / 32)
+        for (int i = tid & 31; i < dk; i += 32)
+            kd[i * GC + t] = t < n ? proj[(size_t)(r0 + t) * ld + (size_t)(H + h) * dk + i] * __expf(b[(n - 1) * dk + i] - b[t * dk + i]) : 0.f;
+    for (int i = tid; i < dk; i += GLA_THREADS) D[((size_t)c * H + h) * dk + i] = __expf(b[(n - 1) * dk + i]);
     __syncthreads();
     const int G = GLA_THREADS / dv;
     if (tid >= G * dv) return;
@@ -198,7 +198,7 @@ gla_chunk_scan_kernel(float *__restrict__ U, const float *__restrict__ D, const 
 // the terms g, g + G, ...: the state is read ONCE, coalesced, straight from global memory; the groups' partial sums are
 // added in group order.
 template <typename TO>
-__global__ void __launch_bounds__(GLA_THREADS)
+__global__ void __launch_bounds__(GLA_THREADS, 3)
 gla_chunk_out_kernel(const float *__restrict__ proj, int ld, const float *__restrict__ z, int ldz, const float *__restrict__ z_bias,
                      const float *__restrict__ norm_w, TO *__restrict__ out, int ldo, const int *__restrict__ chunk_row,
                      const int *__restrict__ chunk_len, const float *__restrict__ P, int H, int dk, int dv, float inv_tau, float q_scale,
@@ -211,15 +211,16 @@ gla_chunk_out_kernel(const float *__restrict__ proj, int ld, const float *__rest
     // b, qs, ks: [GC][dk]; qd: [dk][GC] = q_t * exp(b_t), zero beyond n; AT: [GC (u)][GC (t)] = A[t][u], zero where u > t
     float *b = sm, *qs = b + GC * dk, *ks = qs + GC * dk, *qd = ks + GC * dk, *AT = qd + GC * dk, *part = AT + GC * GC, *os = part + GC * GLA_THREADS, *inv = os + GC * dv;
     gla_cumulative_log_decay(z, ldz, z_bias, r0, n, h, dk, inv_tau, b, tid);
-    for (int e = tid; e < n * dk; e += GLA_THREADS) {
-        const int t = e / dk, i = e - t * dk;
+    const int warp = tid >> 5, lane = tid & 31;
+    for (int t = warp; t < n; t += GLA_THREADS / 32) {
         const float *row = proj + (size_t)(r0 + t) * ld;
-        qs[e] = row[(size_t)h * dk + i] * q_scale;
-        ks[e] = row[(size_t)(H + h) * dk + i];
+        for (int i = lane; i < dk; i += 32) {
+            qs[t * dk + i] = row[(size_t)h * dk + i] * q_scale;
+            ks[t * dk + i] = row[(size_t)(H + h) * dk + i];
+        }
     }
     __syncthreads();
     // scores inside the chunk: A[t][u] = sum_i q_t[i] k_u[i] exp(b_t[i] - b_u[i]) for u <= t; a warp per pair
-    const int warp = tid >> 5, lane = tid & 31;
     for (int pair = warp; pair < GC * GC; pair += GLA_THREADS / 32) {
         const int u = pair / GC, t = pair - u * GC;
         float acc = 0.f;
@@ -228,10 +229,8 @@ gla_chunk_out_kernel(const float *__restrict__ proj, int ld, const float *__rest
         acc = warp_sum(acc);
         if (lane == 0) AT[pair] = acc;
     }
-    for (int e = tid; e < GC * dk; e += GLA_THREADS) {
-        const int i = e / GC, t = e - i * GC;
-        qd[e] = t < n ? qs[t * dk + i] * expf(b[t * dk + i]) : 0.f;
-    }
+    for (int t = warp; t < GC; t += GLA_THREADS / 32)
+        for (int i = lane; i < dk; i += 32) qd[i * GC + t] = t < n ? qs[t * dk + i] * __expf(b[t * dk + i]) : 0.f;
     __syncthreads();
     const int G = GLA_THREADS / dv;
     const bool active = tid < G * dv;
@@ -281,24 +280,21 @@ gla_chunk_out_kernel(const float *__restrict__ proj, int ld, const float *__rest
     }
     __syncthreads();
     // column j's outputs, groups added in order; then the unit norm over the head's values, a warp per token
-    for (int e = tid; e < n * dv; e += GLA_THREADS) {
-        const int t = e / dv, jj = e - t * dv;
-        float o = 0.f;
-        for (int gg = 0; gg < G; gg++) o += part[t * GLA_THREADS + gg * dv + jj];
-        os[e] = o;
-    }
-    __syncthreads();
+    // a warp per token: the column sums in group order, the unit norm over the head's values, the gate
+    (void)os; (void)inv;
     for (int t = warp; t < n; t += GLA_THREADS / 32) {
+        const float *grow = proj + (size_t)(r0 + t) * ld + (size_t)2 * H * dk + (size_t)(H + h) * dv;
         float ss = 0.f;
-        for (int jj = lane; jj < dv; jj += 32) ss = fmaf(os[t * dv + jj], os[t * dv + jj], ss);
+        for (int jj = lane; jj < dv; jj += 32) {
+            float o = 0.f;
+            for (int gg = 0; gg < G; gg++) o += part[t * GLA_THREADS + gg * dv + jj];
+            part[t * GLA_THREADS + jj] = o;                     // group 0's place: read and written by this lane alone
+            ss = fmaf(o, o, ss);
+        }
         ss = warp_sum(ss);
-        if (lane == 0) inv[t] = 1.0f / sqrtf(ss / (float)dv + eps);
-    }
-    __syncthreads();
-    for (int e = tid; e < n * dv; e += GLA_THREADS) {
-        const int t = e / dv, jj = e - t * dv;
-        const float gate = proj[(size_t)(r0 + t) * ld + (size_t)2 * H * dk + (size_t)(H + h) * dv + jj];
-        out[(size_t)(r0 + t) * ldo + (size_t)h * dv + jj] = from_f32<TO>(os[e] * inv[t] * norm_w[jj] * gla_silu(gate));
+        const float inv_t = 1.0f / sqrtf(ss / (float)dv + eps);
+        for (int jj = lane; jj < dv; jj += 32)
+            out[(size_t)(r0 + t) * ldo + (size_t)h * dv + jj] = from_f32<TO>(part[t * GLA_THREADS + jj] * inv_t * norm_w[jj] * gla_silu(grow[jj]));
     }
 }
 
