@@ -246,13 +246,13 @@ head_gemv_kernel(const void *__restrict__ A, int a_dtype, int lda, int a_stride,
     if (TRANSPOSED) {
         n = blockIdx.x * 256 + threadIdx.x;
         if (n >= N) return;
-        // eight weights are on their way before the first of them is used
-        for (int k0 = 0; k0 < K; k0 += 8) {
-            float w[8];
+        // sixteen weights are on their way before the first of them is used
+        for (int k0 = 0; k0 < K; k0 += 16) {
+            float w[16];
 #pragma unroll
-            for (int u = 0; u < 8; u++) w[u] = k0 + u < K ? load_as(W, w_dtype, ((size_t)h * K + k0 + u) * ldw + n) : 0.f;
+            for (int u = 0; u < 16; u++) w[u] = k0 + u < K ? load_as(W, w_dtype, ((size_t)h * K + k0 + u) * ldw + n) : 0.f;
 #pragma unroll
-            for (int u = 0; u < 8; u++) {
+            for (int u = 0; u < 16; u++) {
                 if (k0 + u >= K) break;
 #pragma unroll
                 for (int m = 0; m < HV_ROWS; m++)
@@ -263,12 +263,12 @@ head_gemv_kernel(const void *__restrict__ A, int a_dtype, int lda, int a_stride,
         const int lane = threadIdx.x & 31;
         n = blockIdx.x * 8 + (threadIdx.x >> 5);
         if (n >= N) return;
-        for (int k0 = lane; k0 < K; k0 += 128) {
-            float w[4];
+        for (int k0 = lane; k0 < K; k0 += 256) {
+            float w[8];
 #pragma unroll
-            for (int u = 0; u < 4; u++) w[u] = k0 + 32 * u < K ? load_as(W, w_dtype, ((size_t)h * N + n) * ldw + k0 + 32 * u) : 0.f;
+            for (int u = 0; u < 8; u++) w[u] = k0 + 32 * u < K ? load_as(W, w_dtype, ((size_t)h * N + n) * ldw + k0 + 32 * u) : 0.f;
 #pragma unroll
-            for (int u = 0; u < 4; u++) {
+            for (int u = 0; u < 8; u++) {
                 if (k0 + 32 * u >= K) break;
 #pragma unroll
                 for (int m = 0; m < HV_ROWS; m++)

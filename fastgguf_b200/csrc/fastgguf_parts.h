@@ -12,10 +12,14 @@
  *    "layers":   [{"block": "prenorm", "mixer": PART, "feed_forward": PART, "mixer_norm": PART,
  *                  "feed_forward_norm": PART}, ...],            "feed_forward": null: a layer without one (then
  *                                                               no feed_forward_norm either); optional
- *                                                               "mixer_post_norm", "feed_forward_post_norm": PART
+ *                                                               "mixer_post_norm", "feed_forward_post_norm": PART;
+ *                                                               block "parallel" has no feed_forward_norm
  *    "schedule": [{"layer": 0, "cache_from": null}, ...],      the order in which layers run: an entry may
  *                                                               name a layer twice (a cache of its own each
- *                                                               time) or read an EARLIER entry's cache
+ *                                                               time) or read an EARLIER entry's cache;
+ *                                                               "reenter": true runs the spec's "reentry" part on
+ *                                                               the stream in front of the entry
+ *    "reentry": PART (optional),                                x <- f(x, the embedding's output), role stream_map
  *    "stop_token_ids": [...], "ignored_tensors": ["regex", ...]}
  *   PART = {"kind": "rmsnorm", "params": {...}, "tensors": {"local name": "checkpoint name"}}
  *   A parameter whose value is itself {"kind": ..., "params": ...} is a nested part (the position encoding
@@ -23,7 +27,8 @@
  *
  * Built-in kinds
  *   norm          "rmsnorm"        {size, eps, offset: 0.0}     y = x / rms(x) * (offset + w)
- *   position      "rope"           {head_dim, theta, scaling: null | {rope_type: "llama3", ...},
+ *   position      "rope"           {head_dim, theta, scaling: null | {rope_type: "llama3", ...} | {rope_type: "yarn", factor,
+ *                                   original_max_position_embeddings, beta_fast, beta_slow},
  *                                   rotary_dim: head_dim, layout: "halves" | "adjacent"}
  *   mixer         "gqa_attention"  {hidden_size, n_heads, n_kv_heads, head_dim, position: PART | null,
  *                                   scale: null = 1/sqrt(head_dim), window: null, keep_first: 0,
@@ -32,12 +37,27 @@
  *                                   k_scale: null = 1/sqrt(head_dim), eps}   linear attention with a fixed decay per
  *                                   head, state [heads, head_dim, v_head_dim] float32 per sequence; tensors
  *                                   q/k/v/g/o_proj.weight
+ *                 "gated_linear_attention"  {hidden_size, n_heads, head_dim, v_head_dim, tau, q_scale, eps, decay_rank: from the
+ *                                   checkpoint}   a decay per key channel and token, sigmoid(low-rank(h) + b)^(1/tau); state as
+ *                                   retention's; tensors q/k/v/g/o_proj.weight, decay_down/up.weight, decay_up.bias, norm.weight
+ *                 "sink_attention" {hidden_size, n_heads, n_kv_heads, head_dim, v_head_dim, scale, window: 0, softcap: 0,
+ *                                   conv_taps: 0, bias: false, sink: false, qk_norm: null | "whole", eps, position: PART | null}
+ *                                   grouped-query attention with biases, a short convolution over time (its last inputs are
+ *                                   per-sequence state), norms over the whole of q and of k, adjacent-pair rotation, capped
+ *                                   scores and a sink; tensors q/k/v/o_proj.weight, q/k/v_proj.bias, q/k/v_conv.weight,
+ *                                   q/k_norm.weight, sinks
+ *                 "latent_attention" {hidden_size, n_heads, head_dim, rot_dim, v_head_dim, kv_rank, q_rank, scale, eps,
+ *                                   sink: false, gate: false, position: PART}   keys and values from one latent a token plus a
+ *                                   shared rotated key part (only those are cached); tensors q_down/q_up/kv_down/k_up/v_up/
+ *                                   o_proj/g_proj.weight, q_down_norm/kv_down_norm.weight, sinks
  *   feed_forward  "swiglu"         {hidden_size, d_ff}
  *                 "mlp"            {hidden_size, d_ff, activation: "relu2"}   down(act(up x))
  *                 "moe"            {hidden_size, d_ff, n_experts, top_k, limit, alpha: 1.702, router: "sigmoid_input"}
  *                                   tensors router.weight, experts.<e>.gate/up/down_proj.weight
  *   block         "prenorm"        x += mixer(norm1(x)); x += feed_forward(norm2(x))
  *                 "sandwich"       x += post1(mixer(norm1(x))); x += post2(feed_forward(norm2(x)))
+ *                 "parallel"       x += mixer(norm1(x)) + feed_forward(norm1(x))
+ *   stream_map    "concat_linear"  {hidden_size}   x <- W [x; embedding output], W [E, 2 E]; tensor weight
  *   embedding     "embedding"      {vocab_size, hidden_size, scale: 1.0}
  *   head          "lm_head"        {vocab_size, hidden_size, softcap: null}   logits <- cap tanh(logits / cap)
  *

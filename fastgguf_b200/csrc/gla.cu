@@ -100,24 +100,22 @@ __global__ void gla_chunk_plan_kernel(const int *__restrict__ cu_rows, int n_seq
     }
 }
 
-// b[t][i] = sum_(s <= t) log a_s[i] for the chunk's tokens, into shared memory (row stride dk); one thread a channel.  The
-// chunk's logits are all requested before the first is used (a load per step of the running sum would wait for memory GC times).
+// b[t][i] = sum_(s <= t) log a_s[i] for the chunk's tokens, into shared memory (row stride dk): the logarithms of all
+// (token, channel) pairs at once, a warp a token, then a running sum per channel.  Contains two __syncthreads().
 __device__ __forceinline__ void gla_cumulative_log_decay(const float *__restrict__ z, int ldz, const float *__restrict__ z_bias, int r0, int n,
                                                          int h, int dk, float inv_tau, float *b, int tid) {
+    for (int t = tid >> 5; t < n; t += GLA_THREADS / 32)
+        for (int i = tid & 31; i < dk; i += 32)
+            b[t * dk + i] = log_sigmoid(z[(size_t)(r0 + t) * ldz + (size_t)h * dk + i] + z_bias[(size_t)h * dk + i]) * inv_tau;
+    __syncthreads();
     for (int i = tid; i < dk; i += GLA_THREADS) {
-        const float bias = z_bias[(size_t)h * dk + i];
-        float zz[GC];
-#pragma unroll
-        for (int t = 0; t < GC; t++) zz[t] = t < n ? z[(size_t)(r0 + t) * ldz + (size_t)h * dk + i] : 0.f;
         float run = 0.f;
-#pragma unroll
-        for (int t = 0; t < GC; t++) {
-            if (t < n) {
-                run += log_sigmoid(zz[t] + bias) * inv_tau;
-                b[t * dk + i] = run;
-            }
+        for (int t = 0; t < n; t++) {
+            run += b[t * dk + i];
+            b[t * dk + i] = run;
         }
     }
+    __syncthreads();
 }
 
 // 1. U[c, h] = sum_j (k_j * exp(b_n - b_j)) v_j^T and D[c, h] = exp(b_n).  One block per (chunk, head); thread (g, j) owns
@@ -126,7 +124,7 @@ __device__ __forceinline__ void gla_cumulative_log_decay(const float *__restrict
 __global__ void __launch_bounds__(GLA_THREADS)
 gla_chunk_state_kernel(const float *__restrict__ proj, int ld, const float *__restrict__ z, int ldz, const float *__restrict__ z_bias,
                        const int *__restrict__ chunk_row, const int *__restrict__ chunk_len, float *__restrict__ U, float *__restrict__ D,
-                       int H, int dk, int dv, float inv_tau) {
+                       float *__restrict__ Bg, int H, int dk, int dv, float inv_tau) {
     extern __shared__ __align__(16) float sm[];
     pdl_launch_dependents();
     pdl_wait();
@@ -134,7 +132,8 @@ gla_chunk_state_kernel(const float *__restrict__ proj, int ld, const float *__re
     const int r0 = chunk_row[c], n = chunk_len[c];
     float *b = sm, *kd = b + GC * dk;                          // b: [GC][dk]; kd: [dk][GC], zero beyond the chunk's n tokens
     gla_cumulative_log_decay(z, ldz, z_bias, r0, n, h, dk, inv_tau, b, tid);
-    __syncthreads();
+    // the outputs kernel reads the cumulative decays instead of forming them again
+    for (int e = tid; e < n * dk; e += GLA_THREADS) Bg[((size_t)c * H + h) * GC * dk + e] = b[e];
     // (loops over a [token][channel] tile walk tokens by warp and channels by lane: no division by a run-time size)
     for (int t = tid >> 5; t < GC; t += GLA_THREADS / 32)
         for (int i = tid & 31; i < dk; i += 32)
@@ -201,8 +200,8 @@ template <typename TO>
 __global__ void __launch_bounds__(GLA_THREADS, 3)
 gla_chunk_out_kernel(const float *__restrict__ proj, int ld, const float *__restrict__ z, int ldz, const float *__restrict__ z_bias,
                      const float *__restrict__ norm_w, TO *__restrict__ out, int ldo, const int *__restrict__ chunk_row,
-                     const int *__restrict__ chunk_len, const float *__restrict__ P, int H, int dk, int dv, float inv_tau, float q_scale,
-                     float eps) {
+                     const int *__restrict__ chunk_len, const float *__restrict__ P, const float *__restrict__ Bg, int H, int dk, int dv,
+                     float inv_tau, float q_scale, float eps) {
     extern __shared__ __align__(16) float sm[];
     pdl_launch_dependents();
     pdl_wait();
@@ -210,7 +209,8 @@ gla_chunk_out_kernel(const float *__restrict__ proj, int ld, const float *__rest
     const int r0 = chunk_row[c], n = chunk_len[c];
     // b, qs, ks: [GC][dk]; qd: [dk][GC] = q_t * exp(b_t), zero beyond n; AT: [GC (u)][GC (t)] = A[t][u], zero where u > t
     float *b = sm, *qs = b + GC * dk, *ks = qs + GC * dk, *qd = ks + GC * dk, *AT = qd + GC * dk, *part = AT + GC * GC, *os = part + GC * GLA_THREADS, *inv = os + GC * dv;
-    gla_cumulative_log_decay(z, ldz, z_bias, r0, n, h, dk, inv_tau, b, tid);
+    (void)z; (void)ldz; (void)z_bias; (void)inv_tau;
+    for (int e = tid; e < n * dk; e += GLA_THREADS) b[e] = Bg[((size_t)c * H + h) * GC * dk + e];
     const int warp = tid >> 5, lane = tid & 31;
     for (int t = warp; t < n; t += GLA_THREADS / 32) {
         const float *row = proj + (size_t)(r0 + t) * ld;
@@ -223,9 +223,14 @@ gla_chunk_out_kernel(const float *__restrict__ proj, int ld, const float *__rest
     // scores inside the chunk: A[t][u] = sum_i q_t[i] k_u[i] exp(b_t[i] - b_u[i]) for u <= t; a warp per pair
     for (int pair = warp; pair < GC * GC; pair += GLA_THREADS / 32) {
         const int u = pair / GC, t = pair - u * GC;
+        if (u > t || t >= n) {                                 // the same for the whole warp
+            if (lane == 0) AT[pair] = 0.f;
+            continue;
+        }
         float acc = 0.f;
-        if (u <= t && t < n)
+        {
             for (int i = lane; i < dk; i += 32) acc = fmaf(qs[t * dk + i] * ks[u * dk + i], __expf(b[t * dk + i] - b[u * dk + i]), acc);
+        }
         acc = warp_sum(acc);
         if (lane == 0) AT[pair] = acc;
     }
@@ -336,7 +341,8 @@ extern "C" int fg_gla_chunked_ok(int dk, int dv) {
 }
 
 // n_chunks = sum over sequences of ceil(rows / fg_gla_chunk_tokens()).  plan: scratch of 2 * n_chunks + n_seq + 1 ints;
-// U: scratch [n_chunks, H, dk, dv] float32; D: scratch [n_chunks, H, dk] float32.
+// U: scratch [n_chunks, H, dk, dv] float32; D: scratch [n_chunks, H, dk (1 + chunk tokens)] float32 (the chunks' decays, then the
+// cumulative log decays of their tokens).
 extern "C" int fg_gla_chunked(const float *proj, int ld, const float *z, int ldz, const float *z_bias, const float *norm_w, void *out,
                               int out_dtype, int ldo, const int *cu_rows, const int *slots, float *state, int *plan, float *U, float *D,
                               int n_seq, int n_chunks, int H, int dk, int dv, float tau, float q_scale, float eps, cudaStream_t stream) {
@@ -357,16 +363,18 @@ extern "C" int fg_gla_chunked(const float *proj, int ld, const float *z, int ldz
     const float inv_tau = 1.0f / tau;
     int code = fg_launch(gla_chunk_plan_kernel, dim3(1), dim3(n_seq >= 256 ? 256 : 32), 0, stream, cu_rows, n_seq, chunk_row, chunk_len, seq_chunk0);
     if (code) return code;
+    float *Bg = D + (size_t)n_chunks * H * dk;
     code = fg_launch(gla_chunk_state_kernel, dim3(n_chunks, H), dim3(GLA_THREADS), gla_state_smem(dk, dv), stream, proj, ld, z, ldz, z_bias,
-                     (const int *)chunk_row, (const int *)chunk_len, U, D, H, dk, dv, inv_tau);
+                     (const int *)chunk_row, (const int *)chunk_len, U, D, Bg, H, dk, dv, inv_tau);
     if (code) return code;
     code = fg_launch(gla_chunk_scan_kernel, dim3(n_seq, H, (dk * dv + GLA_THREADS - 1) / GLA_THREADS), dim3(GLA_THREADS), 0, stream, U,
                      (const float *)D, (const int *)seq_chunk0, slots, state, H, dk, dv);
     if (code) return code;
     if (wide)
         return fg_launch(gla_chunk_out_kernel<float>, dim3(n_chunks, H), dim3(GLA_THREADS), gla_out_smem(dk, dv), stream, proj, ld, z, ldz, z_bias,
-                         norm_w, (float *)out, ldo, (const int *)chunk_row, (const int *)chunk_len, (const float *)U, H, dk, dv, inv_tau, q_scale,
-                         eps);
+                         norm_w, (float *)out, ldo, (const int *)chunk_row, (const int *)chunk_len, (const float *)U, (const float *)Bg, H, dk, dv, inv_tau,
+                         q_scale, eps);
     return fg_launch(gla_chunk_out_kernel<bf16>, dim3(n_chunks, H), dim3(GLA_THREADS), gla_out_smem(dk, dv), stream, proj, ld, z, ldz, z_bias,
-                     norm_w, (bf16 *)out, ldo, (const int *)chunk_row, (const int *)chunk_len, (const float *)U, H, dk, dv, inv_tau, q_scale, eps);
+                     norm_w, (bf16 *)out, ldo, (const int *)chunk_row, (const int *)chunk_len, (const float *)U, (const float *)Bg, H, dk, dv, inv_tau,
+                     q_scale, eps);
 }

@@ -199,7 +199,7 @@ public:
             for (int s = 0; s < b.n_seq; s++) n_chunks += (host_cu[s + 1] - host_cu[s] + GC - 1) / GC;
             int *plan = (int *)rt.arena->alloc(((size_t)2 * n_chunks + b.n_seq + 1) * sizeof(int));
             float *U = (float *)rt.arena->alloc((size_t)n_chunks * H_ * dk_ * dv_ * sizeof(float));
-            float *D = (float *)rt.arena->alloc((size_t)n_chunks * H_ * dk_ * sizeof(float));
+            float *D = (float *)rt.arena->alloc((size_t)n_chunks * H_ * dk_ * (1 + GC) * sizeof(float));     // decays and cumulative log decays
             FG_LAUNCH("mix", fg_gla_chunked, proj.ptr<float>(), (int)proj.ld, z.ptr<float>(), (int)z.ld, bias_.t.ptr<float>(), norm_.t.ptr<float>(),
                       y.data, y.dtype, (int)y.ld, b.cu_rows, b.slots, (float *)io.state, plan, U, D, b.n_seq, n_chunks, H_, dk_, dv_, tau_,
                       q_scale_, eps_, rt.stream);
