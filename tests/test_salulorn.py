@@ -133,6 +133,33 @@ def test_mixer_alone(tmp_path, name, dtype):
         assert rel_err(got[r], want[r]) < tol, (name, r)
 
 
+@pytest.mark.parametrize("name", ["long attention, window past a page, head 64", "long latent attention, latent of 64, heads of 128 for whole prompts",
+                                  "attention, all keys, nothing else"])
+def test_a_wide_batch_of_prompts(tmp_path, name):
+    """Four prompts of 5 to 800 tokens in one step, sequences x longest prompt beyond 3,072: the tensor-core attention then runs
+    its form with two sets of softmax warps, in which a row's sink must still count once.  Then one more token each."""
+    case = one_layer(MIXERS[name])
+    d, W = make_model(tmp_path, case, 12, sharp=2.0, sink=2.0)
+    eng = engine_for(d, "bfloat16", max_tokens=4096, max_batch=4)
+    g = torch.Generator().manual_seed(9)
+    lens = [800, 300, 50, 5]
+    layer = case[0]["layers"][0]
+    xs = [torch.randn(n + 1, case[0]["width"], generator=g, dtype=torch.float64) for n in lens]
+    want = [(x + ps.MIXERS[layer["type"]](ps.rms_norm(x, W["l0.norm1"], 1e-5), W, "l0.mix.", layer["mixer"], 1e-5)).numpy() for x in xs]
+    slots = [eng.acquire() for _ in lens]
+    x_all = np.ascontiguousarray(torch.cat([x[:n] for x, n in zip(xs, lens)]).numpy(), dtype=np.float32)
+    got = eng.block_forward(0, list(zip(slots, lens)), x_all)
+    at = 0
+    for b, n in enumerate(lens):
+        for r in (0, 1, n // 2, n - 2, n - 1):
+            assert rel_err(got[at + r], want[b][r]) < 4e-2, (name, b, r)
+        at += n
+    last = np.ascontiguousarray(torch.stack([x[n] for x, n in zip(xs, lens)]).numpy(), dtype=np.float32)
+    got = eng.block_forward(0, [(s, 1) for s in slots], last)
+    for b, n in enumerate(lens):
+        assert rel_err(got[b], want[b][n]) < 4e-2, (name, b, "decoded")
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_parallel_block_adds_both_sublayers(tmp_path, dtype):
     """norm once, mixer and feed-forward both on its output, both added to the stream."""
